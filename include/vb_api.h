@@ -465,6 +465,66 @@ int vb_codec_rmsnorm(float* d_y, const float* d_x, const float* d_w, int B, int 
 int vb_codec_attn_chunk(float* d_out, const float* d_qkv, float* d_cache, int64_t cache_batch_stride, const int64_t* d_pos0,
                         int B, int H, int Hkv, int D, int T, int W, float theta, void* stream);
 
+/* ---- hybrid decoder stacks with an fp32 residual stream (norm_linear.cu, window_attn.cu, linear_attn.cu, moe.cu) ----
+ * dtype arguments: 0 = bf16, 1 = fp32.  Norm weights, router weights, decays and recurrent states are always fp32.
+ * vb_embed_rows_f32:        out[t] = table[ids[t]] widened to fp32
+ * vb_layernorm_f32:         out[t] = (x[r] - mean) / sqrt(var + eps) * w + b with r = rows ? rows[t] : t
+ * vb_postnorm_residual_f32: x[t] += LN(y[t]; w1, b1); if out2: out2[t] = LN(x[t]; w2, b2)
+ * vb_linear:                Y[r][n] = alpha * sum_k X[src(r)][k] W[g][n][k], fp32 accumulation in k order.  groups > 1:
+ *                           group g owns rows row_off[g]..row_off[g+1] (T = upper bound of a group's rows), src(r) =
+ *                           gather ? gather[r] : r.  epilogue 1: W = N gate rows then N up rows, Y = silu(gate) * up */
+int vb_embed_rows_f32(float* d_out, const void* d_table, const int32_t* d_ids, int T, int width, int vocab, int dtype,
+                      void* stream);
+int vb_layernorm_f32(void* d_out, const float* d_x, const float* d_w, const float* d_b, const int32_t* d_rows, int T,
+                     int width, float eps, int out_dtype, void* stream);
+int vb_postnorm_residual_f32(float* d_x, const float* d_y, const float* d_w1, const float* d_b1, void* d_out2,
+                             const float* d_w2, const float* d_b2, int T, int width, float eps, int out_dtype,
+                             void* stream);
+int vb_linear(void* d_out, const void* d_x, const void* d_w, int T, int N, int K, int ldx, int ldo, int in_dtype,
+              int out_dtype, int epilogue, float alpha, const int32_t* d_row_off, const int32_t* d_gather, int groups,
+              long long w_group_stride, void* stream);
+int vb_cast_f32_bf16(void* d_out, const float* d_in, long long n, void* stream);
+/* Sliding-window attention over per-layer pages K [pages][page][G][dim], V [pages][page][G][vdim].
+ * vb_rotary_table:      cs[t] = cos | sin of pos[t] * freq[j], j < half (freq in double)
+ * vb_qkv_rotary_append: from the fp32 projection rows [T][ldp] (q at q_off, k at k_off, v at v_off): rotate the first
+ *                       2 * half dims of every q / k head in (even, odd) pairs, vmix 1: v_first[t] = v, vmix 2:
+ *                       v = (1 - *lambda) v + *lambda v_first[t]; write q [T][H * dim], append k, v at pos[t] of request
+ *                       row_req[t] (its pages are page_indices[page_indptr[b]..])
+ * vb_window_attn:       out[t][h] = softmax over positions max(0, pos - window + 1)..pos of (q . k) * scale, times V, times
+ *                       sigmoid(gate[t][h]) if gate; window <= 0 = no window.  One warp per (row, head).
+ * vb_window_attn_tiled: the same result for prompt portions: tile i covers rows tile_row0[i].. (at most
+ *                       vb_window_attn_tile_rows()) of request tile_req[i], whose rows are consecutive positions */
+int vb_rotary_table(float* d_cs, const int32_t* d_pos, const double* d_freq, int T, int half, void* stream);
+int vb_qkv_rotary_append(const float* d_proj, int ldp, int q_off, int k_off, int v_off, const float* d_cs, int half,
+                         void* d_q_out, void* d_k_cache, void* d_v_cache, const int32_t* d_row_req, const int32_t* d_pos,
+                         const int32_t* d_page_indptr, const int32_t* d_page_indices, int page_size, int T, int H, int G,
+                         int dim, int vdim, int vmix, float* d_v_first, const float* d_lambda, int dtype, void* stream);
+int vb_window_attn(void* d_out, const void* d_q, const void* d_k_cache, const void* d_v_cache, const float* d_gate,
+                   int ld_gate, const int32_t* d_row_req, const int32_t* d_pos, const int32_t* d_page_indptr,
+                   const int32_t* d_page_indices, int T, int H, int G, int dim, int vdim, int page_size, int window,
+                   float scale, int dtype, void* stream);
+int vb_window_attn_tile_rows(void);
+int vb_window_attn_tiled(void* d_out, const void* d_q, const void* d_k_cache, const void* d_v_cache, const float* d_gate,
+                         int ld_gate, const int32_t* d_pos, const int32_t* d_page_indptr, const int32_t* d_page_indices,
+                         const int32_t* d_qo_indptr, const int32_t* d_tile_req, const int32_t* d_tile_row0, int n_tiles,
+                         int T, int H, int G, int dim, int vdim, int page_size, int window, float scale, int dtype,
+                         void* stream);
+/* Linear attention with a scalar decay per head; q, k, v = silu of the projection columns; state fp32
+ * [slots][H][dim][vdim], zero for a request whose first new token has position 0.  single_rows / multi_rows select
+ * the step kernel (requests bringing one token) and the chunked kernel (requests bringing more). */
+int vb_decay_attn(float* d_out, float* d_state, const float* d_proj, int ldp, int q_off, int k_off, int v_off,
+                  const float* d_decay, const int32_t* d_qo_indptr, const int32_t* d_pos, const int32_t* d_slots, int B,
+                  int H, int dim, int vdim, int single_rows, int multi_rows, void* stream);
+int vb_gated_rmsnorm(void* d_out, const float* d_x, const float* d_w, const float* d_gate, int ld_gate, int T, int N,
+                     float eps, int out_dtype, void* stream);
+/* Mixture of experts: routing, grouping by expert, weighted combination (the experts run through vb_linear) */
+int vb_moe_route(int32_t* d_idx, float* d_wts, const void* d_h, const float* d_router_w, const float* d_router_b, int T,
+                 int width, int experts, int top, int h_dtype, void* stream);
+int vb_moe_group(int32_t* d_row_off, int32_t* d_sorted_token, int32_t* d_pair_row, const int32_t* d_idx, int T,
+                 int experts, int top, void* stream);
+int vb_moe_combine(float* d_y, const float* d_expert_out, const float* d_shared_out, const float* d_wts,
+                   const int32_t* d_pair_row, int T, int width, int top, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -103,6 +103,26 @@ SIGNATURES = {
     "vb_codec_rmsnorm": (c_int, [P, P, P, c_int, c_int, c_int, c_float, P]),
     "vb_codec_attn_chunk": (c_int, [P, P, P, c_int64, P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, P]),
     "vb_orpheus_window_codes": (c_int, [P, P, P, P, c_int, c_int, P]),
+    "vb_embed_rows_f32": (c_int, [P, P, P, c_int, c_int, c_int, c_int, P]),
+    "vb_layernorm_f32": (c_int, [P, P, P, P, P, c_int, c_int, c_float, c_int, P]),
+    "vb_postnorm_residual_f32": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_float, c_int, P]),
+    "vb_linear": (c_int, [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, P, P, c_int,
+                          C.c_longlong, P]),
+    "vb_cast_f32_bf16": (c_int, [P, P, C.c_longlong, P]),
+    "vb_rotary_table": (c_int, [P, P, P, c_int, c_int, P]),
+    "vb_qkv_rotary_append": (c_int, [P, c_int, c_int, c_int, c_int, P, c_int, P, P, P, P, P, P, P, c_int, c_int, c_int,
+                                     c_int, c_int, c_int, c_int, P, P, c_int, P]),
+    "vb_window_attn": (c_int, [P, P, P, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                               c_int, P]),
+    "vb_window_attn_tile_rows": (c_int, []),
+    "vb_window_attn_tiled": (c_int, [P, P, P, P, P, c_int, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
+                                     c_int, c_int, c_float, c_int, P]),
+    "vb_decay_attn": (c_int, [P, P, P, c_int, c_int, c_int, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
+                              P]),
+    "vb_gated_rmsnorm": (c_int, [P, P, P, P, c_int, c_int, c_int, c_float, c_int, P]),
+    "vb_moe_route": (c_int, [P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P]),
+    "vb_moe_group": (c_int, [P, P, P, P, c_int, c_int, c_int, P]),
+    "vb_moe_combine": (c_int, [P, P, P, P, P, c_int, c_int, c_int, P]),
 }
 
 _lock = threading.Lock()
@@ -113,26 +133,43 @@ class VoxB200Error(RuntimeError):
     pass
 
 
-def load(build_if_missing: bool = False):
-    """Load the shared library (once).  Never falls back to another implementation."""
+def _absent(name: str):
+    def fn(*_a):
+        raise VoxB200Error(f"{name} is not in the loaded library (a profile build): run `python -m vox_serve_b200.build`")
+    return fn
+
+
+def load(build_if_missing: bool = False, profile: str = None):
+    """Load the shared library (once).  Never falls back to another implementation.  ``profile``: when the full library
+    has not been built, build (if asked) and load the subset library of that profile (build.PROFILES) instead; entry
+    points it lacks raise when called."""
     global _lib
     if _lib is not None:
         return _lib
     with _lock:
         if _lib is not None:
             return _lib
-        if not os.path.exists(LIB_PATH):
-            if build_if_missing:
-                from .build import build
+        path = LIB_PATH
+        if not os.path.exists(path):
+            from .build import build, lib_path
 
-                build()
-            else:
+            if profile is not None:
+                path = lib_path(profile)
+            if build_if_missing:
+                build(profile=profile)
+            elif not os.path.exists(path):
                 raise VoxB200Error(
-                    f"{LIB_PATH} not found: build it with `python -m vox_serve_b200.build` "
+                    f"{path} not found: build it with `python -m vox_serve_b200.build` "
                     "(no CPU / PyTorch fallback exists for this path)")
-        lib = C.CDLL(LIB_PATH)
+        lib = C.CDLL(path)
         for name, (res, args) in SIGNATURES.items():
-            fn = getattr(lib, name)
+            try:
+                fn = getattr(lib, name)
+            except AttributeError:
+                if path == LIB_PATH:
+                    raise
+                setattr(lib, name, _absent(name))
+                continue
             fn.restype, fn.argtypes = res, args
         _lib = lib
     return _lib
@@ -147,7 +184,7 @@ def check(rc: int, what: str = ""):
 # kernels (+ memset nodes) each entry point enqueues; everything not listed launches exactly one
 LAUNCHES = {"vb_set_pdl": 0, "vb_set_trace": 0, "vb_weight_tiles_bytes": 0, "vb_tensor_map_kv": 0,
             "vb_tensor_map_2d_bf16": 0, "vb_device_info": 0, "vb_sample": 1, "vb_update_repetition_cache": 1,
-            "vb_set_gemm_smem_kb": 0}
+            "vb_set_gemm_smem_kb": 0, "vb_window_attn_tile_rows": 0}
 launch_counter = [0]
 
 

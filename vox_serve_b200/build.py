@@ -21,7 +21,11 @@ LIB = os.path.join(LIBDIR, "libvoxb200.so")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
 SOURCES = ["api.cu", "elementwise.cu", "attn.cu", "prefill_attn.cu", "prefill_attn_tc.cu", "kvcopy.cu", "encoder.cu", "gemm.cu", "sampler.cu", "snac.cu", "snac_mma.cu",
-           "multicodebook.cu", "mimi.cu", "codec.cu"]
+           "multicodebook.cu", "mimi.cu", "codec.cu", "norm_linear.cu", "window_attn.cu", "linear_attn.cu", "moe.cu"]
+# subsets of the sources that serve one family of models: a first run that only needs that family compiles only these
+# (into lib/libvoxb200_<profile>.so; entry points of the other sources are absent from it)
+PROFILES = {"text": ["api.cu", "elementwise.cu", "gemm.cu", "sampler.cu", "norm_linear.cu", "window_attn.cu", "linear_attn.cu",
+                     "moe.cu"]}
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC",
@@ -42,13 +46,18 @@ def _stale(target: str, deps) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def lib_path(profile: str = None) -> str:
+    return LIB if profile is None else os.path.join(LIBDIR, f"libvoxb200_{profile}.so")
+
+
+def build(force: bool = False, verbose: bool = False, profile: str = None) -> str:
     os.makedirs(OBJDIR, exist_ok=True)
+    sources, lib = (SOURCES, LIB) if profile is None else (PROFILES[profile], lib_path(profile))
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     headers.append(os.path.join(INCLUDE, "vb_api.h"))
     nvcc = _nvcc()
     jobs = []
-    for src in SOURCES:
+    for src in sources:
         s = os.path.join(CSRC, src)
         o = os.path.join(OBJDIR, src.replace(".cu", ".o"))
         if force or _stale(o, [s] + headers):
@@ -67,15 +76,19 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if jobs:
         with ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 4)) as ex:
             list(ex.map(compile_one, jobs))
-    objs = [os.path.join(OBJDIR, s.replace(".cu", ".o")) for s in SOURCES]
-    if force or jobs or _stale(LIB, objs):
+    objs = [os.path.join(OBJDIR, s.replace(".cu", ".o")) for s in sources]
+    if force or jobs or _stale(lib, objs):
+        # (linked under a temporary name and renamed: another process may be loading the library meanwhile)
+        tmp = f"{lib}.{os.getpid()}.tmp"
         cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "--cudart", "static",
-               "-o", LIB, *objs]
+               "-o", tmp, *objs]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    return LIB
+        os.replace(tmp, lib)
+    return lib
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose=True))
+    prof = next((a.split("=", 1)[1] for a in sys.argv[1:] if a.startswith("--profile=")), None)
+    print(build(force="--force" in sys.argv, verbose=True, profile=prof))

@@ -1,0 +1,236 @@
+// Linear attention with a per-head scalar decay ("lightning" attention): per head the state S [dim][vdim] follows
+//   S_t = decay * S_(t-1) + k_t v_t^T,      o_t = S_t^T q_t
+// with q, k, v = silu of a fused projection's columns.  The state lives in fp32 in a slot per live sequence and is
+// carried from step to step; everything after the projection is fp32.
+//
+//   vb_decay_attn_chunked   prompt portions.  CTA = (request, head, block of value dims).  The portion is walked in chunks
+//                           of C tokens: scores A = (Q K^T) .* decay^(i-j) for j <= i, output O = A V + decay^(i+1) Q S,
+//                           then S <- decay^C S + sum_j decay^(C-1-j) k_j v_j^T.  Only non-negative powers of the decay
+//                           appear, so small decays underflow to zero instead of overflowing.
+//   vb_decay_attn_step      single new tokens: CTA = (request, head, block of value dims), one read and one write of the
+//                           state, the output reduced over the key dims in shared memory.
+//   vb_gated_rmsnorm        rows of concatenated heads: x / sqrt(mean(x^2) + eps) * weight * sigmoid(gate).
+// A request whose first new token has position 0 starts from a zero state (the slot's old content is not read).
+#include "../../include/vb_api.h"
+#define VB_PDL_FAMILY 1
+#include "common.cuh"
+
+namespace vb {
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+
+struct DecayAttnParams {
+  const float* proj;         // [T][ldp]
+  int ldp, q_off, k_off, v_off;
+  float* out;                // [T][H * vdim]
+  float* state;              // [slots][H][dim][vdim]
+  const float* decay;        // [H]
+  const int32_t* qo_indptr;  // [B + 1]
+  const int32_t* pos;        // [T]
+  const int32_t* slots;      // [B]
+  int H, dim, vdim, dvb, chunk, min_rows, max_rows;   // requests with min_rows <= new rows <= max_rows are served
+};
+
+__global__ void __launch_bounds__(256) decay_attn_chunked_kernel(DecayAttnParams p) {
+  extern __shared__ float smf[];
+  pdl_sync();
+  const int b = blockIdx.x, h = blockIdx.y, e0 = blockIdx.z * p.dvb;
+  const int r0 = p.qo_indptr[b], n = p.qo_indptr[b + 1] - r0;
+  if (n < p.min_rows || n > p.max_rows) return;
+  const int C = p.chunk, dk = p.dim, dkp = dk + 1, DV = min(p.dvb, p.vdim - e0);
+  const int dvp = p.dvb + 1;
+  float* Sq = smf;                    // [C][dk + 1]
+  float* Sk = Sq + C * dkp;           // [C][dk + 1]
+  float* Sv = Sk + C * dkp;           // [C][dvb + 1]
+  float* Sa = Sv + C * dvp;           // [C][C + 1]
+  float* Ss = Sa + C * (C + 1);       // [dk][dvb + 1]
+  float* pw = Ss + dk * dvp;          // [C + 1] powers of the decay
+  const int tid = threadIdx.x;
+  const double d = static_cast<double>(p.decay[h]);
+  for (int i = tid; i <= C; i += 256) pw[i] = static_cast<float>(pow(d, static_cast<double>(i)));
+  float* S = p.state + ((static_cast<size_t>(p.slots[b]) * p.H + h) * dk) * p.vdim;
+  const bool fresh = p.pos[r0] == 0;
+  for (int i = tid; i < dk * DV; i += 256) {
+    const int k = i / DV, e = i - k * DV;
+    Ss[k * dvp + e] = fresh ? 0.f : S[static_cast<size_t>(k) * p.vdim + e0 + e];
+  }
+  for (int c0 = 0; c0 < n; c0 += C) {
+    const int L = min(C, n - c0);
+    __syncthreads();
+    for (int i = tid; i < C * dk; i += 256) {
+      const int r = i / dk, k = i - r * dk;
+      float qv = 0.f, kv = 0.f;
+      if (r < L) {
+        const float* row = p.proj + static_cast<size_t>(r0 + c0 + r) * p.ldp + h * dk + k;
+        qv = silu_f(row[p.q_off]);
+        kv = silu_f(row[p.k_off]);
+      }
+      Sq[r * dkp + k] = qv;
+      Sk[r * dkp + k] = kv;
+    }
+    for (int i = tid; i < C * DV; i += 256) {
+      const int r = i / DV, e = i - r * DV;
+      Sv[r * dvp + e] = r < L ? silu_f(p.proj[static_cast<size_t>(r0 + c0 + r) * p.ldp + p.v_off + h * p.vdim + e0 + e]) : 0.f;
+    }
+    __syncthreads();
+    for (int i = tid; i < C * C; i += 256) {
+      const int r = i / C, j = i - r * C;
+      float a = 0.f;
+      if (j <= r && r < L) {
+        const float* qr = Sq + r * dkp;
+        const float* kr = Sk + j * dkp;
+        for (int k = 0; k < dk; ++k) a = fmaf(qr[k], kr[k], a);
+        a *= pw[r - j];
+      }
+      Sa[r * (C + 1) + j] = a;
+    }
+    __syncthreads();
+    for (int i = tid; i < L * DV; i += 256) {
+      const int r = i / DV, e = i - r * DV;
+      float intra = 0.f, inter = 0.f;
+      const float* ar = Sa + r * (C + 1);
+      for (int j = 0; j <= r; ++j) intra = fmaf(ar[j], Sv[j * dvp + e], intra);
+      const float* qr = Sq + r * dkp;
+      for (int k = 0; k < dk; ++k) inter = fmaf(qr[k], Ss[k * dvp + e], inter);
+      p.out[static_cast<size_t>(r0 + c0 + r) * p.H * p.vdim + h * p.vdim + e0 + e] = intra + pw[r + 1] * inter;
+    }
+    __syncthreads();
+    const float dl = pw[L];
+    for (int i = tid; i < dk * DV; i += 256) {
+      const int k = i / DV, e = i - k * DV;
+      float a = 0.f;
+      for (int j = 0; j < L; ++j) a = fmaf(pw[L - 1 - j] * Sk[j * dkp + k], Sv[j * dvp + e], a);
+      Ss[k * dvp + e] = dl * Ss[k * dvp + e] + a;
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < dk * DV; i += 256) {
+    const int k = i / DV, e = i - k * DV;
+    S[static_cast<size_t>(k) * p.vdim + e0 + e] = Ss[k * dvp + e];
+  }
+}
+
+// one new token per request: threads = (key group kg, value dim e); the key dims are strided over the groups
+__global__ void __launch_bounds__(256) decay_attn_step_kernel(DecayAttnParams p) {
+  extern __shared__ float smf[];
+  pdl_sync();
+  const int b = blockIdx.x, h = blockIdx.y, e0 = blockIdx.z * p.dvb;
+  const int r0 = p.qo_indptr[b], n = p.qo_indptr[b + 1] - r0;
+  if (n < p.min_rows || n > p.max_rows) return;
+  const int dk = p.dim, DV = min(p.dvb, p.vdim - e0);
+  float* qs = smf;              // [dk]
+  float* ks = qs + dk;          // [dk]
+  float* red = ks + dk;         // [groups][dvb]
+  const int tid = threadIdx.x, groups = 256 / p.dvb, e = tid % p.dvb, kg = tid / p.dvb;
+  const float dec = p.decay[h];
+  float* S = p.state + ((static_cast<size_t>(p.slots[b]) * p.H + h) * dk) * p.vdim;
+  for (int r = 0; r < n; ++r) {
+    const float* row = p.proj + static_cast<size_t>(r0 + r) * p.ldp;
+    const bool fresh = p.pos[r0 + r] == 0;
+    __syncthreads();
+    for (int k = tid; k < dk; k += 256) {
+      qs[k] = silu_f(row[p.q_off + h * dk + k]);
+      ks[k] = silu_f(row[p.k_off + h * dk + k]);
+    }
+    __syncthreads();
+    float o = 0.f;
+    if (e < DV && kg < groups) {
+      const float v = silu_f(row[p.v_off + h * p.vdim + e0 + e]);
+      for (int k = kg; k < dk; k += groups) {
+        float* sp = S + static_cast<size_t>(k) * p.vdim + e0 + e;
+        const float s = (fresh ? 0.f : dec * *sp) + ks[k] * v;
+        *sp = s;
+        o = fmaf(s, qs[k], o);
+      }
+    }
+    if (kg < groups) red[kg * p.dvb + e] = o;
+    __syncthreads();
+    if (tid < DV) {
+      float t = 0.f;
+      for (int gI = 0; gI < groups; ++gI) t += red[gI * p.dvb + tid];
+      p.out[static_cast<size_t>(r0 + r) * p.H * p.vdim + h * p.vdim + e0 + tid] = t;
+    }
+  }
+}
+
+template <typename OT>
+__global__ void gated_rmsnorm_kernel(OT* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w,
+                                     const float* __restrict__ gate, int ld_gate, int N, float eps) {
+  __shared__ float red[40];
+  pdl_sync();
+  const size_t t = blockIdx.x;
+  const float* row = x + t * N;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < N; i += blockDim.x) q += row[i] * row[i];
+  const int lane = threadIdx.x & 31, wp = threadIdx.x >> 5;
+  q = warp_sum(q);
+  if (lane == 0) red[wp] = q;
+  __syncthreads();
+  if (wp == 0) {
+    float s = lane < (blockDim.x >> 5) ? red[lane] : 0.f;
+    s = warp_sum(s);
+    if (lane == 0) red[32] = s;
+  }
+  __syncthreads();
+  const float rstd = 1.f / sqrtf(red[32] / N + eps);
+  for (int i = threadIdx.x; i < N; i += blockDim.x) {
+    float v = row[i] * rstd * w[i];
+    if (gate) v *= 1.f / (1.f + expf(-gate[t * ld_gate + i]));
+    if constexpr (sizeof(OT) == 4) out[t * N + i] = v;
+    else out[t * N + i] = __float2bfloat16_rn(v);
+  }
+}
+
+static size_t chunked_smem(int C, int dk, int dvb) {
+  return (2ull * C * (dk + 1) + static_cast<size_t>(C) * (dvb + 1) + static_cast<size_t>(C) * (C + 1) +
+          static_cast<size_t>(dk) * (dvb + 1) + C + 1) * sizeof(float);
+}
+
+}  // namespace vb
+
+using namespace vb;
+
+extern "C" {
+
+int vb_decay_attn(float* d_out, float* d_state, const float* d_proj, int ldp, int q_off, int k_off, int v_off,
+                  const float* d_decay, const int32_t* d_qo_indptr, const int32_t* d_pos, const int32_t* d_slots, int B,
+                  int H, int dim, int vdim, int single_rows, int multi_rows, void* stream) {
+  VB_CHECK_ARG(d_out && d_state && d_proj && d_decay && d_qo_indptr && d_pos && d_slots, "vb_decay_attn: null pointer");
+  VB_CHECK_ARG(H > 0 && dim > 0 && vdim > 0, "vb_decay_attn: bad sizes H=%d dim=%d vdim=%d", H, dim, vdim);
+  if (B <= 0) return 0;
+  int dvb = 64;
+  while (dvb > 1 && dvb / 2 >= vdim) dvb /= 2;       // the smallest power of two >= vdim, at most 64
+  DecayAttnParams p{d_proj, ldp, q_off, k_off, v_off, d_out, d_state, d_decay, d_qo_indptr, d_pos, d_slots,
+                    H, dim, vdim, dvb, 0, 0, 0};
+  dim3 grid(B, H, (vdim + dvb - 1) / dvb);
+  if (single_rows) {          // requests that bring exactly one token
+    p.min_rows = 1;
+    p.max_rows = 1;
+    const size_t smem = (2ull * dim + 256) * sizeof(float);
+    VB_CHECK_ARG(smem <= 48 * 1024, "vb_decay_attn: head dim %d too large", dim);
+    VB_LAUNCH_PDL(decay_attn_step_kernel, grid, 256, smem, stream, p);
+  }
+  if (multi_rows) {           // requests that bring a portion of a prompt
+    p.min_rows = 2;
+    p.max_rows = 1 << 30;
+    int C = 64;
+    while (C > 8 && chunked_smem(C, dim, dvb) > 200 * 1024) C /= 2;
+    const size_t smem = chunked_smem(C, dim, dvb);
+    VB_CHECK_ARG(smem <= static_cast<size_t>(VB_MAX_DYN_SMEM), "vb_decay_attn: head dim %d too large", dim);
+    p.chunk = C;
+    VB_CHECK_CUDA(cudaFuncSetAttribute(decay_attn_chunked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+    VB_LAUNCH_PDL(decay_attn_chunked_kernel, grid, 256, smem, stream, p);
+  }
+  return 0;
+}
+
+int vb_gated_rmsnorm(void* d_out, const float* d_x, const float* d_w, const float* d_gate, int ld_gate, int T, int N,
+                     float eps, int out_dtype, void* stream) {
+  VB_CHECK_ARG(d_out && d_x && d_w && N > 0, "vb_gated_rmsnorm: bad arguments");
+  if (T <= 0) return 0;
+  if (out_dtype == 1) VB_LAUNCH_PDL(gated_rmsnorm_kernel<float>, T, 256, 0, stream, static_cast<float*>(d_out), d_x, d_w, d_gate, ld_gate, N, eps);
+  else VB_LAUNCH_PDL(gated_rmsnorm_kernel<__nv_bfloat16>, T, 256, 0, stream, static_cast<__nv_bfloat16*>(d_out), d_x, d_w, d_gate, ld_gate, N, eps);
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,148 @@
+// Mixture-of-experts routing for the hybrid decoder stacks (the expert matrices themselves run through the grouped mode
+// of vb_linear):
+//   vb_moe_route    router logits z = W_r h + b in fp32 (h bf16 or fp32), the `top` largest per token (ties: the lower
+//                   expert index), weights = softmax over the chosen logits only
+//   vb_moe_group    counting sort of the (token, choice) pairs by expert: row_off[E + 1], the token of every sorted row and
+//                   the sorted row of every (token, choice)
+//   vb_moe_combine  y[t] = sum_c weight[t][c] * expert_out[sorted row of (t, c)] (+ shared[t]), summed in choice order so
+//                   that a token's result does not depend on what else is in the batch
+#include "../../include/vb_api.h"
+#define VB_PDL_FAMILY 4
+#include "common.cuh"
+
+namespace vb {
+
+template <typename XT>
+__global__ void __launch_bounds__(128) moe_route_kernel(int32_t* __restrict__ idx, float* __restrict__ wts,
+                                                        const XT* __restrict__ h, const float* __restrict__ wr,
+                                                        const float* __restrict__ br, int W, int E, int top) {
+  extern __shared__ float z[];      // [E]
+  pdl_sync();
+  const size_t t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const XT* x = h + t * W;
+  for (int e = warp; e < E; e += 4) {
+    const float* w = wr + static_cast<size_t>(e) * W;
+    float s = 0.f;
+    for (int i = lane; i < W; i += 32) {
+      float xv;
+      if constexpr (sizeof(XT) == 4) xv = x[i];
+      else xv = __bfloat162float(x[i]);
+      s = fmaf(xv, w[i], s);
+    }
+    s = warp_sum(s);
+    if (lane == 0) z[e] = s + (br ? br[e] : 0.f);
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  // `top` rounds of arg-max over the experts (lane-strided, then across the warp)
+  float chosen_max = 0.f, denom = 0.f, my_val = 0.f;
+  for (int c = 0; c < top; ++c) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = z[e];
+      if (v > best || (v == best && e < bi)) { best = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (c == 0) chosen_max = best;
+    const float ex = expf(best - chosen_max);
+    denom += ex;
+    if (lane == c % 32) my_val = ex;           // (top <= 32)
+    if (lane == 0) {
+      idx[t * top + c] = bi;
+      z[bi] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  if (lane < top) wts[t * top + lane] = my_val / denom;
+}
+
+// single CTA: E <= 1024 experts, any number of pairs
+__global__ void __launch_bounds__(1024) moe_group_kernel(int32_t* __restrict__ row_off, int32_t* __restrict__ sorted_token,
+                                                         int32_t* __restrict__ pair_row, const int32_t* __restrict__ idx,
+                                                         int T, int E, int top) {
+  __shared__ int cnt[1024];
+  __shared__ int base[1025];
+  pdl_sync();
+  const int tid = threadIdx.x, n = T * top;
+  for (int e = tid; e < E; e += 1024) cnt[e] = 0;
+  __syncthreads();
+  for (int i = tid; i < n; i += 1024) atomicAdd(&cnt[idx[i]], 1);
+  __syncthreads();
+  if (tid == 0) {
+    int s = 0;
+    for (int e = 0; e < E; ++e) { base[e] = s; s += cnt[e]; }
+    base[E] = s;
+  }
+  __syncthreads();
+  for (int e = tid; e <= E; e += 1024) row_off[e] = base[e];
+  // rows of an expert in token order: every expert's rows are placed by one thread walking the pairs in order
+  // (deterministic placement; E threads share the scan of n pairs)
+  for (int e = tid; e < E; e += 1024) {
+    int r = base[e];
+    if (cnt[e] == 0) continue;
+    for (int i = 0; i < n; ++i)
+      if (idx[i] == e) {
+        sorted_token[r] = i / top;
+        pair_row[i] = r;
+        ++r;
+      }
+  }
+}
+
+__global__ void moe_combine_kernel(float* __restrict__ y, const float* __restrict__ expert_out,
+                                   const float* __restrict__ shared_out, const float* __restrict__ wts,
+                                   const int32_t* __restrict__ pair_row, int W, int top) {
+  pdl_sync();
+  const size_t t = blockIdx.x;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float a = 0.f;
+    for (int c = 0; c < top; ++c)
+      a = fmaf(wts[t * top + c], expert_out[static_cast<size_t>(pair_row[t * top + c]) * W + i], a);
+    if (shared_out) a += shared_out[t * W + i];
+    y[t * W + i] = a;
+  }
+}
+
+}  // namespace vb
+
+using namespace vb;
+
+extern "C" {
+
+int vb_moe_route(int32_t* d_idx, float* d_wts, const void* d_h, const float* d_router_w, const float* d_router_b, int T,
+                 int width, int experts, int top, int h_dtype, void* stream) {
+  VB_CHECK_ARG(d_idx && d_wts && d_h && d_router_w, "vb_moe_route: null pointer");
+  VB_CHECK_ARG(experts >= 1 && experts <= 1024 && top >= 1 && top <= 32 && top <= experts,
+               "vb_moe_route: experts %d (<= 1024), top %d (<= 32, <= experts)", experts, top);
+  if (T <= 0) return 0;
+  const size_t smem = static_cast<size_t>(experts) * sizeof(float);
+  if (h_dtype == 1) VB_LAUNCH_PDL(moe_route_kernel<float>, T, 128, smem, stream, d_idx, d_wts, static_cast<const float*>(d_h), d_router_w, d_router_b, width, experts, top);
+  else VB_LAUNCH_PDL(moe_route_kernel<__nv_bfloat16>, T, 128, smem, stream, d_idx, d_wts, static_cast<const __nv_bfloat16*>(d_h), d_router_w, d_router_b, width, experts, top);
+  return 0;
+}
+
+int vb_moe_group(int32_t* d_row_off, int32_t* d_sorted_token, int32_t* d_pair_row, const int32_t* d_idx, int T,
+                 int experts, int top, void* stream) {
+  VB_CHECK_ARG(d_row_off && d_sorted_token && d_pair_row && d_idx, "vb_moe_group: null pointer");
+  VB_CHECK_ARG(experts >= 1 && experts <= 1024, "vb_moe_group: experts %d (<= 1024)", experts);
+  if (T <= 0) return 0;
+  VB_LAUNCH_PDL(moe_group_kernel, 1, 1024, 0, stream, d_row_off, d_sorted_token, d_pair_row, d_idx, T, experts, top);
+  return 0;
+}
+
+int vb_moe_combine(float* d_y, const float* d_expert_out, const float* d_shared_out, const float* d_wts,
+                   const int32_t* d_pair_row, int T, int width, int top, void* stream) {
+  VB_CHECK_ARG(d_y && d_expert_out && d_wts && d_pair_row, "vb_moe_combine: null pointer");
+  if (T <= 0) return 0;
+  VB_LAUNCH_PDL(moe_combine_kernel, T, 256, 0, stream, d_y, d_expert_out, d_shared_out, d_wts, d_pair_row, width, top);
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,298 @@
+// Building blocks of the hybrid (attention + linear-attention + mixture-of-experts) decoder stacks whose residual
+// stream is kept in fp32: embedding rows into an fp32 stream, LayerNorm with weight and bias (alone, and fused as
+// "post-norm -> residual add -> next pre-norm"), and a shape-agnostic linear layer Y = X W^T with fp32 accumulation for
+// bf16 or fp32 operands, dense or grouped by expert with gathered input rows.
+//
+// The linear kernel is the any-shape, any-precision path: every output is ONE sequential fp32 FMA chain over k, so a
+// row's result does not depend on which other rows share the launch (batch invariance) and fp32 operands are computed in
+// true fp32.  bf16 projections whose shapes fit the tcgen05 kernel (gemm.cu) are routed there by the engine.
+#include "../../include/vb_api.h"
+#define VB_PDL_FAMILY 4
+#include "common.cuh"
+
+namespace vb {
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  // red: >= 33 floats of shared memory; every thread gets the total
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  if (w == 0) {
+    float t = lane < nw ? red[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+template <typename WT>
+__global__ void embed_rows_kernel(float* __restrict__ out, const WT* __restrict__ table, const int32_t* __restrict__ ids,
+                                  int W, int vocab) {
+  pdl_sync();
+  const int t = blockIdx.x;
+  int id = ids[t];
+  id = min(max(id, 0), vocab - 1);
+  const WT* src = table + static_cast<size_t>(id) * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) out[static_cast<size_t>(t) * W + i] = to_f(src[i]);
+}
+
+// LayerNorm of a row: (x - mean) / sqrt(mean((x - mean)^2) + eps) * w + b, statistics in two passes over the row
+template <typename OT>
+__global__ void layernorm_kernel(OT* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w,
+                                 const float* __restrict__ b, int W, float eps, const int32_t* __restrict__ rows) {
+  extern __shared__ float sm[];
+  float* row = sm;
+  float* red = sm + W;
+  pdl_sync();
+  const int t = blockIdx.x;
+  const size_t src = rows ? static_cast<size_t>(rows[t]) : static_cast<size_t>(t);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) row[i] = x[src * W + i];
+  __syncthreads();
+  float s = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) s += row[i];
+  const float mean = block_sum(s, red) / W;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float d = row[i] - mean;
+    q += d * d;
+  }
+  const float rstd = 1.f / sqrtf(block_sum(q, red) / W + eps);
+  for (int i = threadIdx.x; i < W; i += blockDim.x)
+    out[static_cast<size_t>(t) * W + i] = from_f<OT>((row[i] - mean) * rstd * w[i] + b[i]);
+}
+
+// x[t] += LN(y[t]; w1, b1);  optionally out2[t] = LN(x[t]; w2, b2) (the pre-norm of the sublayer that follows)
+template <typename OT>
+__global__ void postnorm_residual_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ w1,
+                                         const float* __restrict__ b1, OT* __restrict__ out2,
+                                         const float* __restrict__ w2, const float* __restrict__ b2, int W, float eps) {
+  extern __shared__ float sm[];
+  float* row = sm;
+  float* red = sm + W;
+  pdl_sync();
+  const size_t t = blockIdx.x;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) row[i] = y[t * W + i];
+  __syncthreads();
+  float s = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) s += row[i];
+  float mean = block_sum(s, red) / W;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float d = row[i] - mean;
+    q += d * d;
+  }
+  float rstd = 1.f / sqrtf(block_sum(q, red) / W + eps);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = x[t * W + i] + ((row[i] - mean) * rstd * w1[i] + b1[i]);
+    x[t * W + i] = v;
+    row[i] = v;
+  }
+  if (out2 == nullptr) return;
+  __syncthreads();
+  s = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) s += row[i];
+  mean = block_sum(s, red) / W;
+  q = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float d = row[i] - mean;
+    q += d * d;
+  }
+  rstd = 1.f / sqrtf(block_sum(q, red) / W + eps);
+  for (int i = threadIdx.x; i < W; i += blockDim.x)
+    out2[t * W + i] = from_f<OT>((row[i] - mean) * rstd * w2[i] + b2[i]);
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Y[r][n] = alpha * sum_k X[src(r)][k] * W[g][n][k]
+//   dense:   g = 0, r in [0, T), src(r) = r
+//   grouped: blockIdx.z = g, r in [row_off[g], row_off[g + 1]), src(r) = gather ? gather[r] : r
+// epilogue 0: store (OT);  1: W holds N "gate" rows followed by N "up" rows, store silu(gate) * up (OT)
+// Tile 64 x 64, BK 16, 256 threads, 4 x 4 outputs per thread.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int LB_M = 64, LB_N = 64, LB_K = 16;
+
+struct LinearParams {
+  void* out;
+  const void* x;
+  const void* w;
+  const int32_t* row_off;
+  const int32_t* gather;
+  int T, N, K, ldx, ldo, epi;
+  long long w_group_stride;     // elements between the weight matrices of consecutive groups
+  float alpha;
+};
+
+template <typename XT, typename WT, typename OT, int EPI>
+__global__ void __launch_bounds__(256) linear_kernel(LinearParams p) {
+  constexpr int NB = EPI == 1 ? 2 : 1;
+  __shared__ float As[LB_K][LB_M + 4];
+  __shared__ float Bs[NB][LB_K][LB_N + 4];
+  pdl_sync();
+  int r_lo = 0, r_hi = p.T;
+  if (p.row_off) {
+    r_lo = p.row_off[blockIdx.z];
+    r_hi = p.row_off[blockIdx.z + 1];
+  }
+  const int m0 = r_lo + blockIdx.x * LB_M, n0 = blockIdx.y * LB_N;
+  if (m0 >= r_hi) return;
+  const XT* X = static_cast<const XT*>(p.x);
+  const WT* Wm = static_cast<const WT*>(p.w) + static_cast<size_t>(blockIdx.z) * p.w_group_stride;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  // loader: row lr of the tile, 4 consecutive k starting at lk
+  const int lr = tid >> 2, lk = (tid & 3) * 4;
+  const int ar = m0 + lr;
+  const XT* arow = nullptr;
+  if (ar < r_hi) arow = X + static_cast<size_t>(p.gather ? p.gather[ar] : ar) * p.ldx;
+  const int bn = n0 + lr;
+  const WT* brow[NB];
+#pragma unroll
+  for (int h = 0; h < NB; ++h) brow[h] = bn < p.N ? Wm + (static_cast<size_t>(h) * p.N + bn) * p.K : nullptr;
+  float acc[NB][4][4];
+#pragma unroll
+  for (int h = 0; h < NB; ++h)
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[h][i][j] = 0.f;
+  for (int k0 = 0; k0 < p.K; k0 += LB_K) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int k = k0 + lk + u;
+      As[lk + u][lr] = (arow && k < p.K) ? to_f(arow[k]) : 0.f;
+#pragma unroll
+      for (int h = 0; h < NB; ++h) Bs[h][lk + u][lr] = (brow[h] && k < p.K) ? to_f(brow[h][k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < LB_K; ++k) {
+      const float4 a4 = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
+      const float a[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+      for (int h = 0; h < NB; ++h) {
+        const float4 b4 = *reinterpret_cast<const float4*>(&Bs[h][k][tx * 4]);
+        const float b[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[h][i][j] = fmaf(a[i], b[j], acc[h][i][j]);
+      }
+    }
+    __syncthreads();
+  }
+  OT* out = static_cast<OT*>(p.out);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = m0 + ty * 4 + i;
+    if (r >= r_hi) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= p.N) continue;
+      float v;
+      if (EPI == 1) {
+        const float g = acc[0][i][j], u = acc[NB - 1][i][j];
+        v = g / (1.f + expf(-g)) * u;
+      } else {
+        v = acc[0][i][j] * p.alpha;
+      }
+      out[static_cast<size_t>(r) * p.ldo + n] = from_f<OT>(v);
+    }
+  }
+}
+
+template <typename XT, typename WT, typename OT>
+static int launch_linear(const LinearParams& p, int groups, int max_rows, cudaStream_t stream) {
+  dim3 grid((max_rows + LB_M - 1) / LB_M, (p.N + LB_N - 1) / LB_N, groups);
+  if (p.epi == 1) VB_LAUNCH_PDL((linear_kernel<XT, WT, OT, 1>), grid, 256, 0, stream, p);
+  else VB_LAUNCH_PDL((linear_kernel<XT, WT, OT, 0>), grid, 256, 0, stream, p);
+  return 0;
+}
+
+__global__ void cast_f32_bf16_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ in, long long n) {
+  pdl_sync();
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = __float2bfloat16_rn(in[i]);
+}
+
+}  // namespace vb
+
+using namespace vb;
+using bf16 = __nv_bfloat16;
+
+extern "C" {
+
+int vb_embed_rows_f32(float* d_out, const void* d_table, const int32_t* d_ids, int T, int width, int vocab, int dtype,
+                      void* stream) {
+  VB_CHECK_ARG(d_out && d_table && d_ids && width > 0 && vocab > 0, "vb_embed_rows_f32: bad arguments");
+  if (T <= 0) return 0;
+  if (dtype == 1) VB_LAUNCH_PDL(embed_rows_kernel<float>, T, 128, 0, stream, d_out, static_cast<const float*>(d_table), d_ids, width, vocab);
+  else VB_LAUNCH_PDL(embed_rows_kernel<bf16>, T, 128, 0, stream, d_out, static_cast<const bf16*>(d_table), d_ids, width, vocab);
+  return 0;
+}
+
+int vb_layernorm_f32(void* d_out, const float* d_x, const float* d_w, const float* d_b, const int32_t* d_rows, int T,
+                     int width, float eps, int out_dtype, void* stream) {
+  VB_CHECK_ARG(d_out && d_x && d_w && d_b && width > 0, "vb_layernorm_f32: bad arguments");
+  if (T <= 0) return 0;
+  const size_t smem = (static_cast<size_t>(width) + 40) * sizeof(float);
+  VB_CHECK_ARG(smem <= static_cast<size_t>(VB_MAX_DYN_SMEM), "vb_layernorm_f32: width %d too large", width);
+  if (out_dtype == 1) {
+    if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+    VB_LAUNCH_PDL(layernorm_kernel<float>, T, 256, smem, stream, static_cast<float*>(d_out), d_x, d_w, d_b, width, eps, d_rows);
+  } else {
+    if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(layernorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+    VB_LAUNCH_PDL(layernorm_kernel<bf16>, T, 256, smem, stream, static_cast<bf16*>(d_out), d_x, d_w, d_b, width, eps, d_rows);
+  }
+  return 0;
+}
+
+int vb_postnorm_residual_f32(float* d_x, const float* d_y, const float* d_w1, const float* d_b1, void* d_out2,
+                             const float* d_w2, const float* d_b2, int T, int width, float eps, int out_dtype,
+                             void* stream) {
+  VB_CHECK_ARG(d_x && d_y && d_w1 && d_b1 && width > 0, "vb_postnorm_residual_f32: bad arguments");
+  VB_CHECK_ARG(!d_out2 || (d_w2 && d_b2), "vb_postnorm_residual_f32: the second norm needs weight and bias");
+  if (T <= 0) return 0;
+  const size_t smem = (static_cast<size_t>(width) + 40) * sizeof(float);
+  VB_CHECK_ARG(smem <= static_cast<size_t>(VB_MAX_DYN_SMEM), "vb_postnorm_residual_f32: width %d too large", width);
+  if (out_dtype == 1) {
+    if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(postnorm_residual_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+    VB_LAUNCH_PDL(postnorm_residual_kernel<float>, T, 256, smem, stream, d_x, d_y, d_w1, d_b1, static_cast<float*>(d_out2), d_w2, d_b2, width, eps);
+  } else {
+    if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(postnorm_residual_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+    VB_LAUNCH_PDL(postnorm_residual_kernel<bf16>, T, 256, smem, stream, d_x, d_y, d_w1, d_b1, static_cast<bf16*>(d_out2), d_w2, d_b2, width, eps);
+  }
+  return 0;
+}
+
+int vb_linear(void* d_out, const void* d_x, const void* d_w, int T, int N, int K, int ldx, int ldo, int in_dtype,
+              int out_dtype, int epilogue, float alpha, const int32_t* d_row_off, const int32_t* d_gather, int groups,
+              long long w_group_stride, void* stream) {
+  VB_CHECK_ARG(d_out && d_x && d_w && N > 0 && K > 0 && ldx >= K && ldo >= N, "vb_linear: bad arguments");
+  VB_CHECK_ARG(epilogue == 0 || epilogue == 1, "vb_linear: epilogue %d", epilogue);
+  VB_CHECK_ARG(groups >= 1 && (groups == 1 || d_row_off), "vb_linear: grouped launches need row offsets");
+  if (T <= 0) return 0;
+  LinearParams p{d_out, d_x, d_w, d_row_off, d_gather, T, N, K, ldx, ldo, epilogue, w_group_stride, alpha};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // in_dtype: 0 = bf16 activations and weights, 1 = fp32 both; out_dtype likewise
+  if (in_dtype == 1) return out_dtype == 1 ? launch_linear<float, float, float>(p, groups, T, s) : launch_linear<float, float, bf16>(p, groups, T, s);
+  return out_dtype == 1 ? launch_linear<bf16, bf16, float>(p, groups, T, s) : launch_linear<bf16, bf16, bf16>(p, groups, T, s);
+}
+
+int vb_cast_f32_bf16(void* d_out, const float* d_in, long long n, void* stream) {
+  VB_CHECK_ARG(d_out && d_in, "vb_cast_f32_bf16: null pointer");
+  if (n <= 0) return 0;
+  VB_LAUNCH_PDL(cast_f32_bf16_kernel, static_cast<unsigned>((n + 255) / 256), 256, 0, stream, static_cast<bf16*>(d_out), d_in, n);
+  return 0;
+}
+
+}  // extern "C"

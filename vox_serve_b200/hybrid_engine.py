@@ -1,0 +1,415 @@
+"""Decoder stacks that mix softmax attention (sliding window, grouped heads, partial interleaved rotary, cross-layer
+value mixing, sigmoid output gate), linear attention with a per-head decay and a recurrent fp32 state, and
+mixture-of-experts feed-forwards with a shared expert, around an fp32 residual stream with LayerNorm before and after
+every sublayer.  ``LlamaEngine`` (engine.py) is the engine of the Llama-shaped speech LMs; this one is configured layer
+by layer from a ``HybridConfig`` and runs the same way: a fixed sequence of C-ABI launches over preallocated buffers, no
+host synchronisation, CUDA-graph capturable.
+
+One step serves a batch of requests that each bring one or more new tokens (a decoded token, a whole prompt or a portion
+of one).  Per layer:
+    [fused q|k|v|gate projection]  ->  rotary + value mixing + page append  ->  window attention (* gate)  ->  o projection
+    [fused q|k|v|gate projection]  ->  decay attention over the slot's state  ->  gated RMS norm         ->  o projection
+    router -> group by expert -> grouped gate/up (silu * up) -> grouped down -> shared expert -> weighted sum
+each followed by ``x += LayerNorm(y)`` fused with the LayerNorm that feeds the next sublayer.
+
+Precision: ``dtype`` bfloat16 keeps projections' operands, q / k / v, the page cache and the attention output in bf16 with
+fp32 accumulation; norms, softmax, router, residual, recurrent state, decays and the lightning path after its projection
+are fp32.  ``dtype`` float32 runs everything in fp32 (sequential FMA chains, no reduced-precision matrix mode).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+
+from . import ops
+from ._lib import VoxB200Error
+
+BF16, F32, I32 = torch.bfloat16, torch.float32, torch.int32
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# configuration
+# ------------------------------------------------------------------------------------------------------------------
+@dataclass
+class RotaryConfig:
+    dims: int
+    base: float
+    factor: Optional[float] = None       # Llama-3.1 style wavelength-dependent scaling when set
+    low: float = 1.0
+    high: float = 4.0
+    original: float = 8192.0
+
+    def key(self) -> Tuple:
+        return (self.dims, self.base, self.factor, self.low, self.high, self.original)
+
+    def frequencies(self) -> torch.Tensor:
+        """float64 [dims / 2]: base^(-2i/dims); wavelengths above original/low are slowed by ``factor``, those below
+        original/high kept, the band in between interpolated linearly in original/wavelength."""
+        out = []
+        for i in range(self.dims // 2):
+            f = self.base ** (-2.0 * i / self.dims)
+            if self.factor is not None:
+                wl = 2.0 * math.pi / f
+                if wl < self.original / self.high:
+                    pass
+                elif wl > self.original / self.low:
+                    f = f / self.factor
+                else:
+                    s = (self.original / wl - self.low) / (self.high - self.low)
+                    f = (1.0 - s) * f / self.factor + s * f
+            out.append(f)
+        return torch.tensor(out, dtype=torch.float64)
+
+
+@dataclass
+class WindowAttentionConfig:
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    window: int = 0                       # 0: every earlier position is visible
+    rotary: Optional[RotaryConfig] = None
+    v_mix: bool = False
+    gate: bool = True
+
+
+@dataclass
+class DecayAttentionConfig:
+    heads: int
+    dim: int
+    vdim: int
+    decay: List[float] = field(default_factory=list)
+
+
+@dataclass
+class MoEConfig:
+    experts: int
+    top: int
+    ff: int
+    shared_ff: int = 0                    # 0: no shared expert
+
+
+@dataclass
+class HybridLayerConfig:
+    kind: str                             # "attention" | "lightning"
+    mixer: Any
+    mlp: Optional[MoEConfig] = None
+
+
+@dataclass
+class HybridConfig:
+    width: int
+    vocab: int
+    eps: float
+    logit_scale: float
+    layers: List[HybridLayerConfig]
+
+    @classmethod
+    def from_json(cls, c: Dict[str, Any]) -> "HybridConfig":
+        layers = []
+        for L in c["layers"]:
+            m = L["mixer"]
+            kind = L["type"]
+            if kind == "attention":
+                rot = None
+                if m.get("rot"):
+                    r = m["rot"]
+                    sc = r.get("scaling") or {}
+                    rot = RotaryConfig(int(r["dims"]), float(r["base"]), float(sc["factor"]) if sc else None,
+                                       float(sc.get("low", 1.0)), float(sc.get("high", 4.0)),
+                                       float(sc.get("original", 8192)))
+                mask = m.get("mask") or {}
+                mixer = WindowAttentionConfig(int(m["heads"]), int(m.get("kv_heads", m["heads"])), int(m["dim"]),
+                                              int(m.get("vdim", m["dim"])), float(m.get("scale", m["dim"] ** -0.5)),
+                                              int(mask.get("size", 0) or 0), rot, bool(m.get("v_mix", False)))
+            elif kind == "lightning":
+                mixer = DecayAttentionConfig(int(m["heads"]), int(m["dim"]), int(m.get("vdim", m["dim"])),
+                                             [float(d) for d in m["decay"]])
+                if len(mixer.decay) != mixer.heads:
+                    raise VoxB200Error(f"{len(mixer.decay)} decays for {mixer.heads} heads")
+            else:
+                raise VoxB200Error(f"unknown mixer type '{kind}'")
+            mlp = None
+            if L.get("mlp"):
+                f = L["mlp"]
+                if f.get("kind", "moe") != "moe":
+                    raise VoxB200Error(f"unknown feed-forward kind '{f.get('kind')}'")
+                sh = f.get("shared") or {}
+                mlp = MoEConfig(int(f["router"]["experts"]), int(f["router"]["top"]), int(f["expert"]["ff"]),
+                                int(sh.get("ff", 0) or 0))
+            layers.append(HybridLayerConfig(kind, mixer, mlp))
+        return cls(int(c["width"]), int(c["vocab"]), float(c["norm"]["eps"]), float(c.get("logit_scale", 1.0)), layers)
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# weights
+# ------------------------------------------------------------------------------------------------------------------
+class HybridWeights:
+    """Device-resident weights from a name -> tensor mapping with the checkpoint names ``embed``, ``l<i>.norm1[.b]``,
+    ``l<i>.norm1b[.b]``, ``l<i>.norm2[.b]``, ``l<i>.norm2b[.b]``, ``l<i>.mix.{q,k,v,g,o,vmix,norm}``,
+    ``l<i>.mlp.{router,router.b,e<j>.{gate,up,down},shared.{gate,up,down}}``, ``final.norm[.b]``, ``head``.
+    q | k | v | g are concatenated into one projection, gate | up of every expert into one matrix, the experts into
+    [E, ...] stacks.  Matrices take the compute dtype; norm weights, router, decays and mixing coefficients stay fp32."""
+
+    def __init__(self, sd: Dict[str, torch.Tensor], cfg: HybridConfig, dtype: torch.dtype, device):
+        self.cfg, self.dtype, self.device = cfg, dtype, torch.device(device)
+        dev = self.device
+
+        def mat(*names):
+            ts = [sd[n] for n in names]
+            t = ts[0] if len(ts) == 1 else torch.cat([x.reshape(-1, x.shape[-1]) for x in ts], 0)
+            return t.to(device=dev, dtype=dtype).contiguous()
+
+        def vec(name):
+            return sd[name].to(device=dev, dtype=F32).contiguous()
+
+        def norm(name):
+            return vec(name), vec(name + ".b")
+
+        self.embed = mat("embed")
+        self.head = mat("head")
+        self.final_norm = norm("final.norm")
+        if tuple(self.embed.shape) != (cfg.vocab, cfg.width) or tuple(self.head.shape) != (cfg.vocab, cfg.width):
+            raise VoxB200Error("embed / head shapes do not match the configuration")
+        self.layers: List[Dict[str, Any]] = []
+        for i, L in enumerate(cfg.layers):
+            p = f"l{i}."
+            w: Dict[str, Any] = {"norm1": norm(p + "norm1"), "norm1b": norm(p + "norm1b")}
+            m = L.mixer
+            if L.kind == "attention":
+                w["qkvg"] = mat(p + "mix.q", p + "mix.k", p + "mix.v", p + "mix.g")
+                w["o"] = mat(p + "mix.o")
+                if m.v_mix:
+                    w["vmix"] = sd[p + "mix.vmix"].reshape(1).to(device=dev, dtype=F32).contiguous()
+                want = m.heads * m.dim + m.kv_heads * (m.dim + m.vdim) + m.heads * m.vdim
+            else:
+                w["qkvg"] = mat(p + "mix.q", p + "mix.k", p + "mix.v", p + "mix.g")
+                w["o"] = mat(p + "mix.o")
+                w["norm"] = vec(p + "mix.norm")
+                w["decay"] = torch.tensor(m.decay, dtype=torch.float64).to(device=dev, dtype=F32)
+                want = 2 * m.heads * m.dim + 2 * m.heads * m.vdim
+            if tuple(w["qkvg"].shape) != (want, cfg.width):
+                raise VoxB200Error(f"layer {i}: projection shapes {tuple(w['qkvg'].shape)} do not match the configuration")
+            if L.mlp is not None:
+                f = L.mlp
+                w["norm2"], w["norm2b"] = norm(p + "norm2"), norm(p + "norm2b")
+                w["router"] = vec(p + "mlp.router")
+                w["router_b"] = vec(p + "mlp.router.b") if (p + "mlp.router.b") in sd else None
+                w["gu"] = torch.stack([mat(p + f"mlp.e{e}.gate", p + f"mlp.e{e}.up") for e in range(f.experts)]).contiguous()
+                w["down"] = torch.stack([mat(p + f"mlp.e{e}.down") for e in range(f.experts)]).contiguous()
+                if f.shared_ff:
+                    w["s_gu"] = mat(p + "mlp.shared.gate", p + "mlp.shared.up")
+                    w["s_down"] = mat(p + "mlp.shared.down")
+            self.layers.append(w)
+
+    def nbytes(self) -> int:
+        n = 0
+
+        def walk(o):
+            nonlocal n
+            if isinstance(o, torch.Tensor):
+                n += o.numel() * o.element_size()
+            elif isinstance(o, (tuple, list)):
+                for x in o:
+                    walk(x)
+            elif isinstance(o, dict):
+                for x in o.values():
+                    walk(x)
+        walk([self.embed, self.head, self.final_norm, self.layers])
+        return n
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# caches: pages for the attention layers, state slots for the recurrent layers
+# ------------------------------------------------------------------------------------------------------------------
+class HybridCache:
+    """Per attention layer K [pages, page, G, dim] and V [pages, page, G, vdim] in the compute dtype (all layers share
+    one page table: page p of every layer belongs to the same request); per linear-attention layer a state
+    [slots, H, dim, vdim] in fp32.  Pages and slots are handed out by the worker; a slot's state is treated as zero by
+    the kernels when its request starts at position 0, so nothing is cleared on reuse."""
+
+    def __init__(self, cfg: HybridConfig, num_pages: int, page_size: int, num_slots: int, dtype: torch.dtype, device):
+        self.num_pages, self.page_size, self.num_slots, self.dtype = num_pages, page_size, num_slots, dtype
+        self.k: Dict[int, torch.Tensor] = {}
+        self.v: Dict[int, torch.Tensor] = {}
+        self.state: Dict[int, torch.Tensor] = {}
+        for i, L in enumerate(cfg.layers):
+            m = L.mixer
+            if L.kind == "attention":
+                self.k[i] = torch.zeros(num_pages, page_size, m.kv_heads, m.dim, dtype=dtype, device=device)
+                self.v[i] = torch.zeros(num_pages, page_size, m.kv_heads, m.vdim, dtype=dtype, device=device)
+            else:
+                self.state[i] = torch.zeros(num_slots, m.heads, m.dim, m.vdim, dtype=F32, device=device)
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for d in (self.k, self.v, self.state) for t in d.values())
+
+
+@dataclass
+class StepInputs:
+    """Device-side description of one step (all int32): ``ids`` / ``pos`` / ``row_req`` per token row, ``qo_indptr``
+    [B + 1] rows of every request, ``page_indptr`` [B + 1] + ``page_indices`` its pages, ``slots`` [B] its state slot,
+    ``out_rows`` the rows whose logits are computed.  ``multi`` / ``single``: whether any request brings more than one /
+    exactly one token (host knowledge: selects the prompt-portion and the single-token kernels).  ``tiles``: row tiles
+    (tile_req, tile_row0, n_tiles) of the requests that bring several tokens, for the tiled attention kernel."""
+    ids: torch.Tensor
+    pos: torch.Tensor
+    row_req: torch.Tensor
+    qo_indptr: torch.Tensor
+    page_indptr: torch.Tensor
+    page_indices: torch.Tensor
+    slots: torch.Tensor
+    out_rows: torch.Tensor
+    B: int
+    T: int
+    n_out: int
+    multi: bool = True
+    single: bool = True
+    tiles: Optional[Tuple[torch.Tensor, torch.Tensor, int]] = None
+
+
+class HybridEngine:
+    def __init__(self, weights: HybridWeights, cache: HybridCache, max_rows: int, max_out_rows: int):
+        cfg = weights.cfg
+        self.w, self.cfg, self.cache, self.dtype = weights, cfg, cache, weights.dtype
+        self.max_rows, self.max_out_rows = max_rows, max_out_rows
+        dev, R, W, CT = weights.device, max_rows, cfg.width, weights.dtype
+        att = [L.mixer for L in cfg.layers if L.kind == "attention"]
+        lin = [L.mixer for L in cfg.layers if L.kind == "lightning"]
+        moe = [L.mlp for L in cfg.layers if L.mlp is not None]
+        p_att = [m.heads * m.dim + m.kv_heads * (m.dim + m.vdim) + m.heads * m.vdim for m in att]
+        p_lin = [2 * m.heads * (m.dim + m.vdim) for m in lin]
+        hv = max([m.heads * m.vdim for m in att + lin] + [1])
+        self.x = torch.zeros(R, W, dtype=F32, device=dev)              # residual stream
+        self.h = torch.zeros(R, W, dtype=CT, device=dev)               # normed input of the running sublayer
+        self.y = torch.zeros(R, W, dtype=F32, device=dev)              # sublayer output
+        self.proj = torch.zeros(R * max(p_att + p_lin + [1]), dtype=F32, device=dev)
+        self.q = torch.zeros(R * max([m.heads * m.dim for m in att] + [1]), dtype=CT, device=dev)
+        self.mix_out = torch.zeros(R * hv, dtype=CT, device=dev)       # gated mixer output, input of the o projection
+        self.lin_o = torch.zeros(R * hv, dtype=F32, device=dev)        # linear-attention output before its norm
+        self.v_first = torch.zeros(R * max([m.kv_heads * m.vdim for m in att if m.v_mix] + [1]), dtype=F32, device=dev)
+        self.freqs: Dict[Tuple, torch.Tensor] = {}
+        self.cs: Dict[Tuple, torch.Tensor] = {}
+        for m in att:
+            if m.rotary is not None and m.rotary.key() not in self.freqs:
+                if m.rotary.dims > m.dim or m.rotary.dims % 2:
+                    raise VoxB200Error(f"rotary dims {m.rotary.dims} do not fit head dim {m.dim}")
+                self.freqs[m.rotary.key()] = m.rotary.frequencies().to(dev)
+                self.cs[m.rotary.key()] = torch.zeros(R, 2, m.rotary.dims // 2, dtype=F32, device=dev)
+        if moe:
+            top, E = max(f.top for f in moe), max(f.experts for f in moe)
+            self.moe_idx = torch.zeros(R * top, dtype=I32, device=dev)
+            self.moe_wts = torch.zeros(R * top, dtype=F32, device=dev)
+            self.moe_row_off = torch.zeros(E + 1, dtype=I32, device=dev)
+            self.moe_sorted = torch.zeros(R * top, dtype=I32, device=dev)
+            self.moe_pair_row = torch.zeros(R * top, dtype=I32, device=dev)
+            self.moe_act = torch.zeros(R * max(f.top * f.ff for f in moe), dtype=CT, device=dev)
+            self.moe_out = torch.zeros(R * top * W, dtype=F32, device=dev)
+            self.s_act = torch.zeros(R * max([f.shared_ff for f in moe] + [1]), dtype=CT, device=dev)
+            self.s_out = torch.zeros(R, W, dtype=F32, device=dev)
+        self.hn = torch.zeros(max_out_rows, W, dtype=CT, device=dev)
+        self.logits = torch.zeros(max_out_rows, cfg.vocab, dtype=F32, device=dev)
+        self.first_vmix = next((i for i, L in enumerate(cfg.layers) if L.kind == "attention" and L.mixer.v_mix), None)
+        self.layer_tap = None          # set to a list: the residual stream after every layer is appended (tests)
+        self.use_tiled_attention = True
+        self.use_tensor_core_proj = True
+
+    # ---- projections -----------------------------------------------------------------------------------------
+    def _proj(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0) -> torch.Tensor:
+        """out (fp32 or compute dtype) = alpha * x @ w^T."""
+        return ops.linear(x, w, out, alpha=alpha)
+
+    # ---- mixers ----------------------------------------------------------------------------------------------
+    def _attention(self, i: int, m: WindowAttentionConfig, w: Dict[str, Any], s: StepInputs) -> None:
+        T, W = s.T, self.cfg.width
+        nq, nk, nv = m.heads * m.dim, m.kv_heads * m.dim, m.kv_heads * m.vdim
+        P = nq + nk + nv + m.heads * m.vdim
+        proj = self._proj(self.h[:T], w["qkvg"], self.proj[:T * P].view(T, P))
+        cs, half = None, 0
+        if m.rotary is not None:
+            cs, half = self.cs[m.rotary.key()], m.rotary.dims // 2
+        q = self.q[:T * nq].view(T, nq)
+        vmix = 0 if not m.v_mix else (1 if i == self.first_vmix else 2)
+        ops.qkv_rotary_append(proj, 0, nq, nq + nk, cs, half, q, self.cache.k[i], self.cache.v[i], s.row_req, s.pos,
+                              s.page_indptr, s.page_indices, T, m.heads, m.kv_heads, m.dim, m.vdim, vmix,
+                              self.v_first if m.v_mix else None, w.get("vmix") if vmix == 2 else None)
+        out = self.mix_out[:T * m.heads * m.vdim].view(T, m.heads * m.vdim)
+        gate = proj[:, nq + nk + nv:] if m.gate else None
+        tiles = None
+        if s.tiles is not None and self.use_tiled_attention and m.vdim <= 256:
+            tiles = (s.qo_indptr, s.tiles[0], s.tiles[1], s.tiles[2])
+        if tiles is not None and not s.single:
+            ops.window_attn(q, self.cache.k[i], self.cache.v[i], out, gate, s.row_req, s.pos, s.page_indptr, s.page_indices,
+                            T, m.heads, m.kv_heads, m.dim, m.vdim, m.window, m.scale, tiles=tiles)
+        else:
+            # decode rows (and mixed steps: single rows and portions together) on the warp-per-row kernel
+            ops.window_attn(q, self.cache.k[i], self.cache.v[i], out, gate, s.row_req, s.pos, s.page_indptr, s.page_indices,
+                            T, m.heads, m.kv_heads, m.dim, m.vdim, m.window, m.scale)
+        self._proj(out, w["o"], self.y[:T])
+
+    def _lightning(self, i: int, m: DecayAttentionConfig, w: Dict[str, Any], s: StepInputs) -> None:
+        T = s.T
+        nq, nv = m.heads * m.dim, m.heads * m.vdim
+        P = 2 * nq + 2 * nv
+        proj = self._proj(self.h[:T], w["qkvg"], self.proj[:T * P].view(T, P))
+        o = self.lin_o[:T * nv].view(T, nv)
+        ops.decay_attn(proj, 0, nq, 2 * nq, self.cache.state[i], w["decay"], o, s.qo_indptr, s.pos, s.slots, s.B, m.heads,
+                       m.dim, m.vdim, single_rows=s.single, multi_rows=s.multi)
+        out = self.mix_out[:T * nv].view(T, nv)
+        ops.gated_rmsnorm(o, w["norm"], proj[:, 2 * nq + nv:], self.cfg.eps, out)
+        self._proj(out, w["o"], self.y[:T])
+
+    def _moe(self, f: MoEConfig, w: Dict[str, Any], s: StepInputs) -> None:
+        T, W = s.T, self.cfg.width
+        h = self.h[:T]
+        idx, wts = self.moe_idx[:T * f.top], self.moe_wts[:T * f.top]
+        ops.moe_route(h, w["router"], w["router_b"], f.top, idx, wts)
+        ops.moe_group(idx, T, f.experts, f.top, self.moe_row_off, self.moe_sorted, self.moe_pair_row)
+        act = self.moe_act[:T * f.top * f.ff].view(T * f.top, f.ff)
+        ops.linear(h, w["gu"], act, epilogue=1, row_off=self.moe_row_off, gather=self.moe_sorted, rows=T)
+        eo = self.moe_out[:T * f.top * W].view(T * f.top, W)
+        ops.linear(act, w["down"], eo, row_off=self.moe_row_off, rows=T)
+        shared = None
+        if f.shared_ff:
+            sa = self.s_act[:T * f.shared_ff].view(T, f.shared_ff)
+            ops.linear(h, w["s_gu"], sa, epilogue=1)
+            shared = self._proj(sa, w["s_down"], self.s_out[:T])
+        ops.moe_combine(eo, shared, wts, self.moe_pair_row, f.top, self.y[:T])
+
+    # ---- the step --------------------------------------------------------------------------------------------
+    def forward(self, s: StepInputs) -> torch.Tensor:
+        """Runs the step's rows through every layer, appending to the pages and advancing the slots' states; returns the
+        logits of ``s.out_rows`` as fp32 [n_out, vocab] (a view of a static buffer)."""
+        cfg, w, T = self.cfg, self.w, s.T
+        if T > self.max_rows or s.n_out > self.max_out_rows:
+            raise VoxB200Error(f"step of {T} rows / {s.n_out} logit rows exceeds the engine's {self.max_rows} / {self.max_out_rows}")
+        x, h, y = self.x[:T], self.h[:T], self.y[:T]
+        ops.embed_rows_f32(w.embed, s.ids, x)
+        for key, freq in self.freqs.items():
+            ops.rotary_table(s.pos, freq, self.cs[key][:T])
+        eps = cfg.eps
+        n = len(cfg.layers)
+        if n:
+            ops.layernorm_f32(x, *w.layers[0]["norm1"], eps, h)
+        for i, L in enumerate(cfg.layers):
+            lw = w.layers[i]
+            if L.kind == "attention":
+                self._attention(i, L.mixer, lw, s)
+            else:
+                self._lightning(i, L.mixer, lw, s)
+            nxt = w.layers[i + 1]["norm1"] if i + 1 < n else None
+            if L.mlp is not None:
+                ops.postnorm_residual_f32(x, y, *lw["norm1b"], eps, h, *lw["norm2"])
+                self._moe(L.mlp, lw, s)
+                ops.postnorm_residual_f32(x, y, *lw["norm2b"], eps, *((h,) + nxt if nxt else (None, None, None)))
+            else:
+                ops.postnorm_residual_f32(x, y, *lw["norm1b"], eps, *((h,) + nxt if nxt else (None, None, None)))
+            if self.layer_tap is not None:
+                self.layer_tap.append(x.clone())
+        hn = self.hn[:s.n_out]
+        ops.layernorm_f32(self.x, *w.final_norm, eps, hn, rows=s.out_rows)
+        return ops.linear(hn, w.head, self.logits[:s.n_out], alpha=cfg.logit_scale)

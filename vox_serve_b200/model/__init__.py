@@ -1,15 +1,19 @@
 """Model-adapter registry with the reference's public surface (``vox_serve/model/__init__.py:17-179``):
 ``MODEL_REGISTRY``, ``get_model_class``, ``load_model``, ``register_model``, ``list_supported_models``.
 Only adapters whose whole decode + vocoder path runs on the sm_100a kernels are registered: Orpheus (+ SNAC) and CSM
-(+ Mimi) and Qwen3-TTS (+ its streaming 12 Hz codec decoder)."""
+(+ Mimi) and Qwen3-TTS (+ its streaming 12 Hz codec decoder), and the text-only Bobavik LM.  A model given as a local
+directory is matched by the ``architecture`` of its ``config.json`` first, by its name otherwise."""
 from __future__ import annotations
 
+import json
+import os
 from typing import Any, Dict, Type
 
 import torch
 
 from ..sampling import SamplingConfig
 from .base import BaseLM, BaseLMWithDepth, PreprocessOutput
+from .bobavik import BobavikModel
 from .csm import CSMModel
 from .orpheus import OrpheusModel
 from .qwen3_tts import Qwen3TTSModel
@@ -21,10 +25,20 @@ MODEL_REGISTRY: Dict[str, Type[BaseLM]] = {
     "sesame/csm-1b": CSMModel,
     "qwen3-tts": Qwen3TTSModel,
     "qwen/qwen3-tts": Qwen3TTSModel,
+    "bobavik": BobavikModel,
 }
 
 
 def get_model_class(model_name: str) -> Type[BaseLM]:
+    cfg_path = os.path.join(model_name, "config.json")
+    if os.path.isfile(cfg_path):
+        try:
+            with open(cfg_path) as f:
+                arch = str(json.load(f).get("architecture", "")).lower()
+        except (OSError, ValueError):
+            arch = ""
+        if arch in MODEL_REGISTRY:
+            return MODEL_REGISTRY[arch]
     key = model_name.lower()
     if key in MODEL_REGISTRY:
         return MODEL_REGISTRY[key]

@@ -903,3 +903,166 @@ def orpheus_window_codes(ids: torch.Tensor, audio_id_base: int):
     call("vb_orpheus_window_codes", c0.data_ptr(), c1.data_ptr(), c2.data_ptr(), ids.data_ptr(), B,
          int(audio_id_base), _stream())
     return c0, c1, c2
+
+
+# ----------------------------------------------------------------------------------------------
+# hybrid decoder stacks with an fp32 residual stream (norm_linear.cu, window_attn.cu, linear_attn.cu, moe.cu)
+# dtype codes of the C ABI: 0 = bf16, 1 = fp32
+# ----------------------------------------------------------------------------------------------
+F32 = torch.float32
+
+
+def _dt(x) -> int:
+    d = x if isinstance(x, torch.dtype) else x.dtype
+    if d == BF16:
+        return 0
+    if d == F32:
+        return 1
+    raise VoxB200Error(f"dtype {d}: the hybrid kernels take bfloat16 or float32")
+
+
+def embed_rows_f32(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out [T, W] fp32 = table[ids] (table bf16 or fp32)."""
+    _need_cuda(table, ids, out)
+    assert ids.dtype == torch.int32 and out.dtype == F32 and table.is_contiguous() and out.is_contiguous()
+    call("vb_embed_rows_f32", out.data_ptr(), table.data_ptr(), ids.data_ptr(), ids.numel(), table.shape[1],
+         table.shape[0], _dt(table), _stream())
+    return out
+
+
+def layernorm_f32(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, eps: float, out: torch.Tensor,
+                  rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = LayerNorm(x[rows[t] if rows is given else t]) * w + b; x, w, b fp32; out bf16 or fp32."""
+    _need_cuda(x, w, b, out)
+    assert x.dtype == F32 and w.dtype == F32 and b.dtype == F32 and x.is_contiguous() and out.is_contiguous()
+    T = out.shape[0]
+    call("vb_layernorm_f32", out.data_ptr(), x.data_ptr(), w.data_ptr(), b.data_ptr(), _p(rows), T, x.shape[1], float(eps),
+         _dt(out), _stream())
+    return out
+
+
+def postnorm_residual_f32(x: torch.Tensor, y: torch.Tensor, w1: torch.Tensor, b1: torch.Tensor, eps: float,
+                          out2: Optional[torch.Tensor] = None, w2: Optional[torch.Tensor] = None,
+                          b2: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x += LayerNorm(y; w1, b1) in place (fp32); with out2 also out2 = LayerNorm(x; w2, b2), bf16 or fp32."""
+    _need_cuda(x, y, w1, b1)
+    assert x.dtype == F32 and y.dtype == F32 and x.shape == y.shape and x.is_contiguous() and y.is_contiguous()
+    call("vb_postnorm_residual_f32", x.data_ptr(), y.data_ptr(), w1.data_ptr(), b1.data_ptr(), _p(out2), _p(w2), _p(b2),
+         x.shape[0], x.shape[1], float(eps), _dt(out2) if out2 is not None else 1, _stream())
+    return x
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0, alpha: float = 1.0,
+           row_off: Optional[torch.Tensor] = None, gather: Optional[torch.Tensor] = None,
+           rows: Optional[int] = None) -> torch.Tensor:
+    """out [R, N] = alpha * x @ w^T with fp32 accumulation.  x [T, K] and w ([N, K], or [E, N, K] with row_off
+    [E + 1] for experts) share a dtype (bf16 or fp32); out bf16 or fp32.  epilogue 1: w holds N gate rows then N up rows
+    (per expert) and out = silu(gate) * up.  gather: int32 source row of x for every output row.  rows: how many rows a
+    group can have at most (grouped) / how many rows to compute (dense); default x.shape[0]."""
+    _need_cuda(x, w, out)
+    assert x.dtype == w.dtype and x.stride(-1) == 1 and w.is_contiguous() and out.stride(-1) == 1
+    groups = w.shape[0] if w.dim() == 3 else 1
+    n_rows_w, K = w.shape[-2], w.shape[-1]
+    N = n_rows_w // 2 if epilogue == 1 else n_rows_w
+    assert x.shape[1] == K and out.shape[1] >= N
+    T = x.shape[0] if rows is None else rows
+    call("vb_linear", out.data_ptr(), x.data_ptr(), w.data_ptr(), T, N, K, x.stride(0), out.stride(0), _dt(x), _dt(out),
+         epilogue, float(alpha), _p(row_off), _p(gather), groups, n_rows_w * K, _stream())
+    return out
+
+
+def cast_f32_bf16(src: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    _need_cuda(src, out)
+    assert src.dtype == F32 and out.dtype == BF16 and src.is_contiguous() and out.is_contiguous() and src.numel() == out.numel()
+    call("vb_cast_f32_bf16", out.data_ptr(), src.data_ptr(), src.numel(), _stream())
+    return out
+
+
+def rotary_table(pos: torch.Tensor, freq: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out [T, 2, half] fp32 = cos | sin of pos[t] * freq[j]; freq float64 [half]."""
+    _need_cuda(pos, freq, out)
+    assert pos.dtype == torch.int32 and freq.dtype == torch.float64 and out.dtype == F32
+    call("vb_rotary_table", out.data_ptr(), pos.data_ptr(), freq.data_ptr(), pos.numel(), freq.numel(), _stream())
+    return out
+
+
+def qkv_rotary_append(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, cs: Optional[torch.Tensor], half: int,
+                      q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, row_req: torch.Tensor,
+                      pos: torch.Tensor, page_indptr: torch.Tensor, page_indices: torch.Tensor, T: int, H: int, G: int,
+                      dim: int, vdim: int, vmix: int = 0, v_first: Optional[torch.Tensor] = None,
+                      lam: Optional[torch.Tensor] = None) -> None:
+    """proj fp32 [T, ld]; k_cache [pages, page, G, dim], v_cache [pages, page, G, vdim] (bf16 or fp32, as q_out)."""
+    _need_cuda(proj, q_out, k_cache, v_cache)
+    assert proj.dtype == F32 and k_cache.dtype == q_out.dtype == v_cache.dtype
+    call("vb_qkv_rotary_append", proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, _p(cs), half, q_out.data_ptr(),
+         k_cache.data_ptr(), v_cache.data_ptr(), row_req.data_ptr(), pos.data_ptr(), page_indptr.data_ptr(),
+         page_indices.data_ptr(), k_cache.shape[1], T, H, G, dim, vdim, vmix, _p(v_first), _p(lam), _dt(q_out), _stream())
+
+
+def window_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                gate: Optional[torch.Tensor], row_req: torch.Tensor, pos: torch.Tensor, page_indptr: torch.Tensor,
+                page_indices: torch.Tensor, T: int, H: int, G: int, dim: int, vdim: int, window: int, scale: float,
+                tiles: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor, int]] = None) -> torch.Tensor:
+    """gate: an fp32 view [T, H * vdim] (any row stride) or None.  tiles = (qo_indptr, tile_req, tile_row0, n_tiles):
+    run the shared-memory tiled kernel over those row tiles instead of one warp per row."""
+    _need_cuda(q, k_cache, v_cache, out)
+    ld_gate = gate.stride(0) if gate is not None else 0
+    if tiles is None:
+        call("vb_window_attn", out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _p(gate), ld_gate,
+             row_req.data_ptr(), pos.data_ptr(), page_indptr.data_ptr(), page_indices.data_ptr(), T, H, G, dim, vdim,
+             k_cache.shape[1], int(window), float(scale), _dt(q), _stream())
+    else:
+        qo, tile_req, tile_row0, n_tiles = tiles
+        call("vb_window_attn_tiled", out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _p(gate),
+             ld_gate, pos.data_ptr(), page_indptr.data_ptr(), page_indices.data_ptr(), qo.data_ptr(), tile_req.data_ptr(),
+             tile_row0.data_ptr(), n_tiles, T, H, G, dim, vdim, k_cache.shape[1], int(window), float(scale), _dt(q),
+             _stream())
+    return out
+
+
+def window_attn_tile_rows() -> int:
+    return _lib.load().vb_window_attn_tile_rows()
+
+
+def decay_attn(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, state: torch.Tensor, decay: torch.Tensor,
+               out: torch.Tensor, qo_indptr: torch.Tensor, pos: torch.Tensor, slots: torch.Tensor, B: int, H: int, dim: int,
+               vdim: int, single_rows: bool = True, multi_rows: bool = True) -> torch.Tensor:
+    """Linear attention with per-head decay over the fp32 projection rows; state fp32 [slots, H, dim, vdim]."""
+    _need_cuda(proj, state, decay, out)
+    assert proj.dtype == F32 and state.dtype == F32 and decay.dtype == F32 and out.dtype == F32 and state.is_contiguous()
+    call("vb_decay_attn", out.data_ptr(), state.data_ptr(), proj.data_ptr(), proj.stride(0), q_off, k_off, v_off,
+         decay.data_ptr(), qo_indptr.data_ptr(), pos.data_ptr(), slots.data_ptr(), B, H, dim, vdim, int(single_rows),
+         int(multi_rows), _stream())
+    return out
+
+
+def gated_rmsnorm(x: torch.Tensor, w: torch.Tensor, gate: Optional[torch.Tensor], eps: float, out: torch.Tensor):
+    """out = x / sqrt(mean(x^2) + eps) * w * sigmoid(gate); x, w, gate fp32 (gate: a view with any row stride)."""
+    _need_cuda(x, w, out)
+    assert x.dtype == F32 and w.dtype == F32 and x.is_contiguous() and out.is_contiguous()
+    call("vb_gated_rmsnorm", out.data_ptr(), x.data_ptr(), w.data_ptr(), _p(gate), gate.stride(0) if gate is not None else 0,
+         x.shape[0], x.shape[1], float(eps), _dt(out), _stream())
+    return out
+
+
+def moe_route(h: torch.Tensor, router_w: torch.Tensor, router_b: Optional[torch.Tensor], top: int, idx: torch.Tensor,
+              wts: torch.Tensor) -> None:
+    """idx int32 [T, top], wts fp32 [T, top]; router_w fp32 [E, W]."""
+    _need_cuda(h, router_w, idx, wts)
+    assert router_w.dtype == F32 and idx.dtype == torch.int32 and wts.dtype == F32 and h.is_contiguous()
+    call("vb_moe_route", idx.data_ptr(), wts.data_ptr(), h.data_ptr(), router_w.data_ptr(), _p(router_b), h.shape[0],
+         h.shape[1], router_w.shape[0], top, _dt(h), _stream())
+
+
+def moe_group(idx: torch.Tensor, T: int, experts: int, top: int, row_off: torch.Tensor, sorted_token: torch.Tensor,
+              pair_row: torch.Tensor) -> None:
+    call("vb_moe_group", row_off.data_ptr(), sorted_token.data_ptr(), pair_row.data_ptr(), idx.data_ptr(), T, experts, top,
+         _stream())
+
+
+def moe_combine(expert_out: torch.Tensor, shared_out: Optional[torch.Tensor], wts: torch.Tensor, pair_row: torch.Tensor,
+                top: int, out: torch.Tensor) -> torch.Tensor:
+    assert expert_out.dtype == F32 and out.dtype == F32 and expert_out.is_contiguous() and out.is_contiguous()
+    call("vb_moe_combine", out.data_ptr(), expert_out.data_ptr(), _p(shared_out), wts.data_ptr(), pair_row.data_ptr(),
+         out.shape[0], out.shape[1], top, _stream())
+    return out

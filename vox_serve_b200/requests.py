@@ -50,6 +50,10 @@ class Request:
     eos_injected: bool = False
     chunk_send_timestamps: List[float] = field(default_factory=list)
     chunk_durations: List[float] = field(default_factory=list)
+    # ---- prompts fed in portions (text worker) ----
+    pending_tokens: Optional[List[int]] = None      # token ids still to be fed: the rest of the prompt, or given continuations
+    step_tokens: Optional[int] = None               # how many of them the next step takes (None: the worker's portion size)
+    logit_rows: Optional[List[int]] = None          # places within the next step's tokens whose logits are kept
 
 
 class LMInputs(TypedDict):

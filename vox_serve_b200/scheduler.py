@@ -16,8 +16,15 @@ from .requests import Request
 
 class Scheduler:
     def __init__(self, worker, max_batch_size: Optional[int] = None, one_prefill_per_step: bool = True,
-                 on_audio: Optional[Callable[[Request, bytes, float], None]] = None, vocoder_batch_steps: int = 1):
+                 on_audio: Optional[Callable[[Request, bytes, float], None]] = None, vocoder_batch_steps: int = 1,
+                 prefill_chunk_tokens: Optional[int] = None):
         self.model_worker = worker
+        # workers that feed prompts in portions (worker/text.py): at most this many prompt tokens of a request per step, so
+        # that a long prompt shares its steps with the decoding requests instead of holding them up (None: whole prompts)
+        if prefill_chunk_tokens is not None:
+            if not hasattr(worker, "prefill_chunk_tokens"):
+                raise ValueError("this worker runs whole prompts: prefill_chunk_tokens is an option of the text worker")
+            worker.prefill_chunk_tokens = int(prefill_chunk_tokens)
         # 1 = the reference's schedule (every request is vocoded in the step its window completes).  N > 1 holds
         # completed windows back until every N-th step so that the vocoder runs on a full batch: with staggered
         # requests the per-step batches are ~batch/7 windows and the early decoder stages cost as much for 5 windows
@@ -162,7 +169,8 @@ class Scheduler:
                 except StopIteration:
                     break
         if self.trace is not None:
-            self.trace.append([(r.request_id, int(r.lm_output_tokens[-1][0, 0])) for r in lm_requests])
+            self.trace.append([(r.request_id, int(r.lm_output_tokens[-1][0, 0]) if r.lm_output_tokens else None)
+                               for r in lm_requests])
         self.steps += 1
         return len(lm_requests), len(detokenize_requests)
 

@@ -40,12 +40,13 @@ class _Staging:
     qo_indptr[B+1] | kv_indptr[B+1] | last_page_len[B] | slots[B] | position[T] | host_ids[T] | row_slot[T] |
     kv_indices[P].  Offsets are fixed by (max_req, max_rows) so CUDA graphs can bake the device pointers."""
 
-    def __init__(self, max_req: int, max_rows: int, max_pages: int, device):
+    def __init__(self, max_req: int, max_rows: int, max_pages: int, device, extra=()):
+        """extra: further (name, length) int32 fields, laid out after the common ones."""
         self.max_req, self.max_rows, self.max_pages = max_req, max_rows, max_pages
         o = 0
         self.off = {}
         for name, n in (("qo", max_req + 1), ("indptr", max_req + 1), ("last", max_req), ("slots", max_req),
-                        ("pos", max_rows), ("ids", max_rows), ("row_slot", max_rows), ("indices", max_pages)):
+                        ("pos", max_rows), ("ids", max_rows), ("row_slot", max_rows), ("indices", max_pages)) + tuple(extra):
             self.off[name] = (o, n)
             o += (n + 3) // 4 * 4
         self.n = o
@@ -75,6 +76,7 @@ class _Staging:
 
 class ModelWorker:
     _serves_depth = False
+    _serves_text = False
 
     def __init__(self, model_name: str, max_batch_size: int, max_num_pages: int, page_size: int, top_p: float = None,
                  top_k: int = None, min_p: float = None, temperature: float = None, max_tokens: int = None,
@@ -83,6 +85,7 @@ class ModelWorker:
                  detokenizer_device: Optional[str] = None, dp_rank: int = 0, dp_size: int = 1,
                  detokenize_interval: int = None, model=None, max_prefill_tokens: int = 1024, **model_kwargs):
         _lib.load()          # fail loudly here, not at the first step, if the CUDA library is absent
+        self.max_logit_rows = int(model_kwargs.pop("max_logit_rows", 0) or 0)     # text worker: tapped logit rows per step
         if not torch.cuda.is_available():
             raise VoxB200Error("ModelWorker needs a CUDA device: there is no CPU path")
         if detokenizer_device not in (None, "cuda", "cuda:0", f"cuda:{torch.cuda.current_device()}"):
@@ -112,6 +115,13 @@ class ModelWorker:
         import logging
 
         self.logger = logging.getLogger(__name__)
+        if getattr(self.model, "is_text_model", False) and not self._serves_text:
+            # text-only LMs (no codec; KV pages plus a recurrent-state slot per request; prompts in portions)
+            from .text import TextModelWorker
+
+            self.__class__ = TextModelWorker
+        elif self._serves_text and not getattr(self.model, "is_text_model", False):
+            raise VoxB200Error("TextModelWorker serves text-only LMs")
         if self.model.has_depth_transformer and not self._serves_depth:
             # the reference builds ``CudaGraphWorker(model_name, ...)`` for every model (scheduler/base.py:57-77); the
             # multi-codebook step lives in a subclass here, selected once the model is known
