@@ -209,7 +209,6 @@ class TextModelWorker(CudaGraphWorker):
                           out_rows=st.d("out_rows", n_out), B=B, T=T, n_out=n_out, multi=multi, single=single,
                           tiles=(st.d("tile_req"), st.d("tile_row0"), n_tiles) if n_tiles else None)
         logits = m.forward(step, engine=self.engine)
-        self.last_logits = logits
         slots = st.d("slots", B)
         out = self.out_ids[:B]
         sl = ops.cast_f32_bf16(logits[:B], self.sample_logits[:B])
@@ -220,8 +219,11 @@ class TextModelWorker(CudaGraphWorker):
     def step_logits(self, request_id: str) -> torch.Tensor:
         """fp32 [tapped rows, vocab] of the request's ``logit_rows`` in the step that ran last (host tensor)."""
         idx = self._logit_index[request_id]
-        sel = torch.as_tensor(idx, dtype=torch.int64, device=self.last_logits.device)
-        return self.last_logits.index_select(0, sel).cpu()
+        buf = self.engine.logits          # (the static buffer, not a step's view of it: decode graphs replay without one)
+        if any(not 0 <= i < buf.shape[0] for i in idx):
+            raise VoxB200Error("logit row outside the engine's buffer")
+        sel = torch.as_tensor(idx, dtype=torch.int64, device=buf.device)
+        return buf.index_select(0, sel).cpu()
 
     # ---- tokens out ---------------------------------------------------------------------------------------------
     def run_detokenize(self, requests: List[Request]):
