@@ -1,0 +1,162 @@
+"""Prefill and decode throughput of the Bobavik design (hybrid engine) beside the Llama-shaped engine of the speech LMs at
+equal size: same width, layer count, head count and head size, and a dense feed-forward as wide as the experts a token
+uses (top * ff + shared ff).  Random weights, a few layers of a real model's shape.
+
+    python bench.py --arch bobavik [--arch-sizes 2048,3072] [--steps K] [--warmup W]
+
+Per size and engine: prefill of one 1024-token prompt (eager launches) and one decode step of 32 requests at context 512
+(a CUDA-graph replay, as served), timed with CUDA events after warm-up; an L2-sized buffer is overwritten between timed
+iterations.  Output: one JSON line per size.
+"""
+from __future__ import annotations
+
+import json
+
+import torch
+
+PROMPT, BATCH, CONTEXT, LAYERS, VOCAB = 1024, 32, 512, 4, 32000
+
+
+def bobavik_config(width: int, ff: int, experts: int = 8, top: int = 2, window: int = 4096) -> dict:
+    heads = width // 128
+    att = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "v_mix": True,
+           "mask": {"size": window}, "rot": {"dims": 64, "base": 1e6,
+                                             "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    lin = {"heads": heads, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** -(5 + 3 * h / heads) for h in range(heads)]}
+    mlp = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff}, "shared": {"ff": ff}}
+    kinds = ["attention", "lightning", "lightning", "attention"]
+    return {"architecture": "Bobavik", "width": width, "vocab": VOCAB, "norm": {"eps": 1e-6}, "logit_scale": 1.0,
+            "layers": [{"type": k, "mixer": dict(att if k == "attention" else lin), "mlp": dict(mlp)}
+                       for k in (kinds * LAYERS)[:LAYERS]]}
+
+
+def _timed(fn, steps: int, warmup: int, flush: torch.Tensor) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(steps):
+        flush.add_(1)                                   # > L2: evicts what the last iteration left there
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        total += a.elapsed_time(b)
+    return total / steps
+
+
+def _graph(fn):
+    torch.cuda.synchronize()
+    g, s = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(g, stream=s):
+            fn()
+    torch.cuda.current_stream().wait_stream(s)
+    return g.replay
+
+
+def bench_bobavik(width: int, ff: int, steps: int, warmup: int, flush) -> dict:
+    from vox_serve_b200 import ops
+    from vox_serve_b200.hybrid_engine import StepInputs
+    from vox_serve_b200.model.bobavik import BobavikModel
+
+    cfg = bobavik_config(width, ff)
+    model = BobavikModel("bobavik-synthetic:1", config=cfg, device="cuda:0")
+    page = 64
+    pages_per_req = (CONTEXT + page) // page + 1
+    n_pages = max(BATCH * pages_per_req, PROMPT // page + 1)
+    cache = model.make_cache(n_pages, page, BATCH)
+    eng = model.make_engine(cache, max(PROMPT, BATCH), BATCH)
+    dev, I32 = "cuda", torch.int32
+
+    def step(n_req: int, rows_per_req: int, pos0: int, per_req_pages: int, tiled: bool):
+        T = n_req * rows_per_req
+        ids = torch.randint(0, VOCAB, (T,), device=dev, dtype=I32)
+        pos = (torch.arange(rows_per_req, device=dev, dtype=I32) + pos0).repeat(n_req)
+        row_req = torch.arange(n_req, device=dev, dtype=I32).repeat_interleave(rows_per_req)
+        qo = torch.arange(n_req + 1, device=dev, dtype=I32) * rows_per_req
+        indptr = torch.arange(n_req + 1, device=dev, dtype=I32) * per_req_pages
+        indices = torch.arange(n_req * per_req_pages, device=dev, dtype=I32)
+        tiles = None
+        if tiled:
+            R = ops.window_attn_tile_rows()
+            r0 = torch.arange(0, T, R, device=dev, dtype=I32)
+            tiles = (torch.div(r0, rows_per_req, rounding_mode="floor").to(I32), r0, r0.numel())
+        return StepInputs(ids=ids, pos=pos, row_req=row_req, qo_indptr=qo, page_indptr=indptr, page_indices=indices,
+                          slots=torch.arange(n_req, device=dev, dtype=I32), out_rows=(qo[1:] - 1).contiguous(), B=n_req, T=T,
+                          n_out=n_req, multi=rows_per_req > 1, single=rows_per_req == 1, tiles=tiles)
+
+    pre = step(1, PROMPT, 0, PROMPT // page + 1, True)
+    t_pre = _timed(lambda: eng.forward(pre), steps, warmup, flush)
+    dec = step(BATCH, 1, CONTEXT, pages_per_req, False)
+    eng.forward(dec)
+    t_dec = _timed(_graph(lambda: eng.forward(dec)), steps, warmup, flush)
+    return {"prefill_ms": t_pre, "prefill_tok_s": PROMPT / t_pre * 1e3, "decode_ms": t_dec,
+            "decode_tok_s": BATCH / t_dec * 1e3, "weight_gb": model.weights.nbytes() / 1e9}
+
+
+def bench_llama(width: int, inter: int, steps: int, warmup: int, flush) -> dict:
+    from vox_serve_b200 import ops
+    from vox_serve_b200.engine import LlamaDims, LlamaEngine, LlamaWeights
+    from vox_serve_b200.model.orpheus import synthetic_state_dict
+
+    heads = width // 128
+    dims = LlamaDims(width, LAYERS, heads, max(1, heads // 4), 128, inter, VOCAB)
+    w = LlamaWeights.from_state_dict(synthetic_state_dict(dims, 1, "cuda"), dims, "cuda")
+    page = 64
+    pages_per_req = (CONTEXT + page) // page + 1
+    n_pages = max(BATCH * pages_per_req, PROMPT // page + 1)
+    kv = torch.zeros(LAYERS, n_pages, 2, page, dims.num_key_value_heads, 128, dtype=torch.bfloat16, device="cuda")
+    eng = LlamaEngine(w, kv, page, max_rows=PROMPT + 64)
+    dev, I32 = "cuda", torch.int32
+
+    def prefill():
+        ids = torch.randint(0, VOCAB, (PROMPT,), device=dev, dtype=I32)
+        pos = torch.arange(PROMPT, device=dev, dtype=I32)
+        qo = torch.tensor([0, PROMPT], device=dev, dtype=I32)
+        indptr = torch.tensor([0, PROMPT // page], device=dev, dtype=I32)
+        indices = torch.arange(PROMPT // page, device=dev, dtype=I32)
+        last = torch.tensor([page], device=dev, dtype=I32)
+        last_rows = torch.tensor([PROMPT - 1], device=dev, dtype=I32)
+
+        def run():
+            ops.plan_rows(eng.plan, qo, indptr, indices, last, 1, PROMPT, page, eng.chunk)
+            eng.forward(ids, pos, PROMPT, last_rows=last_rows)
+        return run
+
+    def decode():
+        ids = torch.randint(0, VOCAB, (BATCH,), device=dev, dtype=I32)
+        pos = torch.full((BATCH,), CONTEXT, device=dev, dtype=I32)
+        indptr = torch.arange(BATCH + 1, device=dev, dtype=I32) * pages_per_req
+        indices = torch.arange(BATCH * pages_per_req, device=dev, dtype=I32)
+        last = torch.full((BATCH,), (CONTEXT + 1) % page or page, device=dev, dtype=I32)
+
+        def run():
+            ops.plan_rows(eng.plan, None, indptr, indices, last, BATCH, BATCH, page, eng.chunk)
+            eng.forward(ids, pos, BATCH)
+        return run
+
+    t_pre = _timed(prefill(), steps, warmup, flush)
+    d = decode()
+    d()
+    t_dec = _timed(_graph(d), steps, warmup, flush)
+    return {"prefill_ms": t_pre, "prefill_tok_s": PROMPT / t_pre * 1e3, "decode_ms": t_dec,
+            "decode_tok_s": BATCH / t_dec * 1e3, "weight_gb": w.nbytes() / 1e9}
+
+
+def run(sizes, steps: int, warmup: int, only: str = "") -> None:
+    flush = torch.zeros(192 << 20, dtype=torch.uint8, device="cuda")
+    for width in sizes:
+        ff = width                     # expert width; a token uses top (2) experts + the shared one
+        line = {"bench": "bobavik_vs_llama", "width": width, "layers": LAYERS, "prompt": PROMPT, "decode_batch": BATCH,
+                "context": CONTEXT, "steps": steps, "warmup": warmup, "dtype": "bf16", "data": "synthetic",
+                "l2": "192 MiB buffer overwritten between timed iterations"}
+        if only in ("", "bobavik"):
+            line["bobavik"] = bench_bobavik(width, ff, steps, warmup, flush)
+        if only in ("", "llama"):
+            line["llama"] = bench_llama(width, 3 * ff, steps, warmup, flush)
+        print(json.dumps(line), flush=True)
+        torch.cuda.empty_cache()

@@ -155,9 +155,13 @@ class HybridWeights:
     q | k | v | g are concatenated into one projection, gate | up of every expert into one matrix, the experts into
     [E, ...] stacks.  Matrices take the compute dtype; norm weights, router, decays and mixing coefficients stay fp32."""
 
-    def __init__(self, sd: Dict[str, torch.Tensor], cfg: HybridConfig, dtype: torch.dtype, device):
+    def __init__(self, sd: Dict[str, torch.Tensor], cfg: HybridConfig, dtype: torch.dtype, device,
+                 tensor_core: bool = True):
         self.cfg, self.dtype, self.device = cfg, dtype, torch.device(device)
         dev = self.device
+        # bf16 dense projections (q|k|v|gate, o, shared expert, output head) are re-tiled for the tcgen05 kernel of gemm.cu
+        # when their reduction size allows its 16-byte rows; the row-major copy is then dropped
+        self.tensor_core = bool(tensor_core) and dtype == BF16 and self.device.type == "cuda"
 
         def mat(*names):
             ts = [sd[n] for n in names]
@@ -170,10 +174,25 @@ class HybridWeights:
         def norm(name):
             return vec(name), vec(name + ".b")
 
+        def dense(t):
+            if self.tensor_core and t.shape[1] % 8 == 0:
+                return ops.pack_weight(t, 128)
+            return t
+
+        def gate_up(gate_name, up_name):
+            """shared expert: [gate rows | up rows] for vb_linear, or gate / up interleaved per tile for the tcgen05 kernel's
+            silu(gate) * up epilogue"""
+            if self.tensor_core and sd[gate_name].shape[1] % 8 == 0:
+                half = ops.gate_up_tile_half(sd[gate_name].shape[0])
+                return ops.pack_weight(ops.interleave_gate_up(mat(gate_name), mat(up_name), half), 2 * half)
+            return mat(gate_name, up_name)
+
         self.embed = mat("embed")
-        self.head = mat("head")
+        self.head = dense(mat("head"))
         self.final_norm = norm("final.norm")
-        if tuple(self.embed.shape) != (cfg.vocab, cfg.width) or tuple(self.head.shape) != (cfg.vocab, cfg.width):
+        # the tcgen05 kernel has no output scale: logit_scale is folded into the final norm's weight and bias there
+        self.final_norm_scaled = tuple(t * cfg.logit_scale for t in self.final_norm)
+        if tuple(self.embed.shape) != (cfg.vocab, cfg.width) or tuple(sd["head"].shape) != (cfg.vocab, cfg.width):
             raise VoxB200Error("embed / head shapes do not match the configuration")
         self.layers: List[Dict[str, Any]] = []
         for i, L in enumerate(cfg.layers):
@@ -194,6 +213,7 @@ class HybridWeights:
                 want = 2 * m.heads * m.dim + 2 * m.heads * m.vdim
             if tuple(w["qkvg"].shape) != (want, cfg.width):
                 raise VoxB200Error(f"layer {i}: projection shapes {tuple(w['qkvg'].shape)} do not match the configuration")
+            w["qkvg"], w["o"] = dense(w["qkvg"]), dense(w["o"])
             if L.mlp is not None:
                 f = L.mlp
                 w["norm2"], w["norm2b"] = norm(p + "norm2"), norm(p + "norm2b")
@@ -202,8 +222,8 @@ class HybridWeights:
                 w["gu"] = torch.stack([mat(p + f"mlp.e{e}.gate", p + f"mlp.e{e}.up") for e in range(f.experts)]).contiguous()
                 w["down"] = torch.stack([mat(p + f"mlp.e{e}.down") for e in range(f.experts)]).contiguous()
                 if f.shared_ff:
-                    w["s_gu"] = mat(p + "mlp.shared.gate", p + "mlp.shared.up")
-                    w["s_down"] = mat(p + "mlp.shared.down")
+                    w["s_gu"] = gate_up(p + "mlp.shared.gate", p + "mlp.shared.up")
+                    w["s_down"] = dense(mat(p + "mlp.shared.down"))
             self.layers.append(w)
 
     def nbytes(self) -> int:
@@ -211,7 +231,9 @@ class HybridWeights:
 
         def walk(o):
             nonlocal n
-            if isinstance(o, torch.Tensor):
+            if isinstance(o, ops.PackedWeight):
+                n += o.logical_bytes()
+            elif isinstance(o, torch.Tensor):
                 n += o.numel() * o.element_size()
             elif isinstance(o, (tuple, list)):
                 for x in o:
@@ -316,11 +338,14 @@ class HybridEngine:
         self.first_vmix = next((i for i, L in enumerate(cfg.layers) if L.kind == "attention" and L.mixer.v_mix), None)
         self.layer_tap = None          # set to a list: the residual stream after every layer is appended (tests)
         self.use_tiled_attention = True
-        self.use_tensor_core_proj = True
 
     # ---- projections -----------------------------------------------------------------------------------------
     def _proj(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0) -> torch.Tensor:
-        """out (fp32 or compute dtype) = alpha * x @ w^T."""
+        """out (fp32) = alpha * x @ w^T: the tcgen05 kernel for packed bf16 weights, the fp32-FMA kernel otherwise."""
+        if isinstance(w, ops.PackedWeight):
+            assert alpha == 1.0 and out.dtype == F32 and out.is_contiguous()
+            ops.gemm(x, w, mode=1, split_k=1, out=out.view(1, x.shape[0], w.N))
+            return out
         return ops.linear(x, w, out, alpha=alpha)
 
     # ---- mixers ----------------------------------------------------------------------------------------------
@@ -376,7 +401,10 @@ class HybridEngine:
         shared = None
         if f.shared_ff:
             sa = self.s_act[:T * f.shared_ff].view(T, f.shared_ff)
-            ops.linear(h, w["s_gu"], sa, epilogue=1)
+            if isinstance(w["s_gu"], ops.PackedWeight):
+                ops.gemm(h, w["s_gu"], mode=2, out=sa, tile_rows=w["s_gu"].tile_rows, n_out=f.shared_ff)
+            else:
+                ops.linear(h, w["s_gu"], sa, epilogue=1)
             shared = self._proj(sa, w["s_down"], self.s_out[:T])
         ops.moe_combine(eo, shared, wts, self.moe_pair_row, f.top, self.y[:T])
 
@@ -411,5 +439,8 @@ class HybridEngine:
             if self.layer_tap is not None:
                 self.layer_tap.append(x.clone())
         hn = self.hn[:s.n_out]
+        if isinstance(w.head, ops.PackedWeight):
+            ops.layernorm_f32(self.x, *w.final_norm_scaled, eps, hn, rows=s.out_rows)
+            return self._proj(hn, w.head, self.logits[:s.n_out])
         ops.layernorm_f32(self.x, *w.final_norm, eps, hn, rows=s.out_rows)
-        return ops.linear(hn, w.head, self.logits[:s.n_out], alpha=cfg.logit_scale)
+        return self._proj(hn, w.head, self.logits[:s.n_out], alpha=cfg.logit_scale)

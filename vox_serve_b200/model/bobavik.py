@@ -55,13 +55,13 @@ def read_safetensors(path: str) -> Dict[str, torch.Tensor]:
     return out
 
 
-def synthetic_state_dict(cfg: HybridConfig, seed: int = 0) -> Dict[str, torch.Tensor]:
-    """Seeded random weights with the checkpoint's names (CPU, bf16 matrices)."""
-    g = torch.Generator().manual_seed(seed)
+def synthetic_state_dict(cfg: HybridConfig, seed: int = 0, device="cpu") -> Dict[str, torch.Tensor]:
+    """Seeded random weights with the checkpoint's names (bf16 matrices), generated on ``device``."""
+    g = torch.Generator(device=device).manual_seed(seed)
     W = cfg.width
 
     def rnd(*shape, std=1.0, mean=0.0):
-        return (torch.randn(*shape, generator=g) * std + mean).to(torch.bfloat16)
+        return (torch.randn(*shape, generator=g, device=device) * std + mean).to(torch.bfloat16)
 
     sd = {"embed": rnd(cfg.vocab, W), "head": rnd(cfg.vocab, W, std=W ** -0.5), "final.norm": rnd(W, std=0.1, mean=1.0),
           "final.norm.b": rnd(W, std=0.1)}
@@ -75,7 +75,7 @@ def synthetic_state_dict(cfg: HybridConfig, seed: int = 0) -> Dict[str, torch.Te
             sd[p + "mix.v"], sd[p + "mix.g"] = rnd(m.kv_heads * m.vdim, W, std=s), rnd(m.heads * m.vdim, W, std=s)
             sd[p + "mix.o"] = rnd(W, m.heads * m.vdim, std=(m.heads * m.vdim) ** -0.5)
             if m.v_mix:
-                sd[p + "mix.vmix"] = torch.rand((), generator=g).to(torch.bfloat16)
+                sd[p + "mix.vmix"] = torch.rand((), generator=g, device=device).to(torch.bfloat16)
         else:
             sd[p + "mix.q"], sd[p + "mix.k"] = rnd(m.heads * m.dim, W, std=s), rnd(m.heads * m.dim, W, std=s)
             sd[p + "mix.v"], sd[p + "mix.g"] = rnd(m.heads * m.vdim, W, std=s), rnd(m.heads * m.vdim, W, std=s)
@@ -99,7 +99,8 @@ class BobavikModel(BaseLM):
     def __init__(self, model_name: str, dtype: torch.dtype = torch.bfloat16, device: str = "cuda:0",
                  enable_torch_compile: bool = False, audio_decoder_device: Optional[str] = None,
                  state_dict: Optional[Dict[str, torch.Tensor]] = None, config: Optional[Dict[str, Any]] = None,
-                 max_tokens: Optional[int] = None, stop_token_id: Optional[int] = None, **_unused):
+                 max_tokens: Optional[int] = None, stop_token_id: Optional[int] = None,
+                 tensor_core_projections: bool = True, **_unused):
         if dtype not in (torch.bfloat16, torch.float32):
             raise VoxB200Error(f"Bobavik runs in bfloat16 or float32, not {dtype}")
         super().__init__(model_name, device, dtype, enable_torch_compile, audio_decoder_device)
@@ -112,14 +113,14 @@ class BobavikModel(BaseLM):
                 state_dict = read_safetensors(os.path.join(model_name, "model.safetensors"))
             elif model_name.startswith("bobavik-synthetic") and config is not None:
                 seed = int(model_name.split(":")[1]) if ":" in model_name else 0
-                state_dict = synthetic_state_dict(HybridConfig.from_json(config), seed)
+                state_dict = synthetic_state_dict(HybridConfig.from_json(config), seed, device)
             else:
                 raise VoxB200Error(f"'{model_name}': pass a directory with config.json + model.safetensors, "
                                    "state_dict= and config=, or 'bobavik-synthetic[:seed]' with config=")
         if config is None:
             raise VoxB200Error("BobavikModel needs its configuration (config=)")
         self.config = HybridConfig.from_json(config) if isinstance(config, dict) else config
-        self.weights = HybridWeights(state_dict, self.config, dtype, device)
+        self.weights = HybridWeights(state_dict, self.config, dtype, device, tensor_core=tensor_core_projections)
         self._max_tokens = max_tokens or 4096
         self.stop_token_id = -1 if stop_token_id is None else stop_token_id
         self.default_sampling_config = SamplingConfig(greedy=True)
