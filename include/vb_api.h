@@ -515,6 +515,15 @@ int vb_window_attn_tiled(void* d_out, const void* d_q, const void* d_k_cache, co
 int vb_decay_attn(float* d_out, float* d_state, const float* d_proj, int ldp, int q_off, int k_off, int v_off,
                   const float* d_decay, const int32_t* d_qo_indptr, const int32_t* d_pos, const int32_t* d_slots, int B,
                   int H, int dim, int vdim, int single_rows, int multi_rows, void* stream);
+/* sequence-parallel form for prompt portions: tiles of vb_decay_attn_tile_rows() rows (0: head sizes too large, use
+ * vb_decay_attn), tile i = rows tile_row0[i].. of request tile_req[i], a request's tiles consecutive and in batch order,
+ * requests bringing a single row have none (run them with vb_decay_attn, single_rows); scratch fp32
+ * [n_tiles][H][dim][vdim] */
+int vb_decay_attn_tile_rows(int dim, int vdim);
+int vb_decay_attn_tiled(float* d_out, float* d_state, float* d_scratch, const float* d_proj, int ldp, int q_off, int k_off,
+                        int v_off, const float* d_decay, const int32_t* d_qo_indptr, const int32_t* d_pos,
+                        const int32_t* d_slots, const int32_t* d_tile_req, const int32_t* d_tile_row0, int n_tiles, int B,
+                        int H, int dim, int vdim, void* stream);
 int vb_gated_rmsnorm(void* d_out, const float* d_x, const float* d_w, const float* d_gate, int ld_gate, int T, int N,
                      float eps, int out_dtype, void* stream);
 /* Mixture of experts: routing, grouping by expert, weighted combination (the experts run through vb_linear) */
@@ -522,6 +531,10 @@ int vb_moe_route(int32_t* d_idx, float* d_wts, const void* d_h, const float* d_r
                  int width, int experts, int top, int h_dtype, void* stream);
 int vb_moe_group(int32_t* d_row_off, int32_t* d_sorted_token, int32_t* d_pair_row, const int32_t* d_idx, int T,
                  int experts, int top, void* stream);
+/* dense form (bf16): act [T][ld] holds silu(gate) * up of EVERY expert side by side (expert e at columns e * ff ..), then
+ * the shared expert's; columns of expert e are scaled by the token's routing weight for e, or zeroed if e was not chosen */
+int vb_moe_scale_dense(void* d_act, const int32_t* d_idx, const float* d_wts, int T, int ld, int experts, int ff, int top,
+                       void* stream);
 int vb_moe_combine(float* d_y, const float* d_expert_out, const float* d_shared_out, const float* d_wts,
                    const int32_t* d_pair_row, int T, int width, int top, void* stream);
 

@@ -277,11 +277,21 @@ def _attention_case(window, n_tokens, page_size, hot, dtype, tiled, H=2, G=1, dk
 @pytest.mark.parametrize("tiled", [False, True])
 @pytest.mark.parametrize("dtype", [F32, BF16])
 def test_window_edges_and_far_keys(tiled, dtype):
+    _window_edges(tiled, dtype, 2, 1)
+
+
+@pytest.mark.gpu
+def test_window_edges_large_head_group():
+    """20 query heads on one key/value head: beyond the grouped kernel's registers, served by the warp-per-head kernel."""
+    _window_edges(False, F32, 20, 1)
+
+
+def _window_edges(tiled, dtype, H, G):
     """the hot key dominates exactly the queries whose window holds it: visible at distance window - 1, gone at distance
     window; with no window it is seen from hundreds of positions away, across page borders."""
     tol = 1e-3 if dtype == F32 else 3e-2
     for window, hot, T, ps in ((16, 5, 70, 8), (33, 31, 130, 16), (0, 3, 300, 8), (64, 64, 200, 64), (1, 7, 20, 4)):
-        got, ref = _attention_case(window, T, ps, hot, dtype, tiled)
+        got, ref = _attention_case(window, T, ps, hot, dtype, tiled, H=H, G=G)
         assert torch.allclose(got.double(), ref, rtol=tol, atol=tol * 10), (window, hot)
         sees = got[:, 0, 0] > 500
         for i in range(T):
@@ -290,8 +300,9 @@ def test_window_edges_and_far_keys(tiled, dtype):
 
 
 @pytest.mark.gpu
-def test_decay_attention_portions_and_state_slots():
-    """chunked and single-token kernels against the recurrence: portions that end inside chunks, decays from 1 down to
+@pytest.mark.parametrize("parallel", [False, True])
+def test_decay_attention_portions_and_state_slots(parallel):
+    """chunked (walked in order, or its tiles in parallel) and single-token kernels against the recurrence: portions that end inside chunks, decays from 1 down to
     values whose powers underflow, a slot that held another sequence before, two requests in one launch."""
     from vox_serve_b200 import ops
 
@@ -315,8 +326,19 @@ def test_decay_attention_portions_and_state_slots():
             out = torch.zeros(2 * c, H * dv, dtype=F32, device=DEV)
             qo = torch.tensor([0, c, 2 * c], dtype=I32, device=DEV)
             pos = torch.cat([torch.arange(lo, lo + c), torch.arange(lo, lo + c)]).to(I32).to(DEV)
-            ops.decay_attn(proj, 0, H * dk, 2 * H * dk, state, dec, out, qo, pos, torch.tensor([2, 0], dtype=I32, device=DEV),
-                           2, H, dk, dv, single_rows=c == 1, multi_rows=c > 1)
+            slots = torch.tensor([2, 0], dtype=I32, device=DEV)
+            if parallel and c > 1:
+                R = ops.decay_attn_tile_rows(dk, dv)
+                assert R == 64
+                r0 = [t0 for base in (0, c) for t0 in range(base, base + c, R)]
+                treq = [0 if t0 < c else 1 for t0 in r0]
+                scratch = torch.full((len(r0) * H * dk * dv,), float("nan"), dtype=F32, device=DEV)
+                ops.decay_attn_tiled(proj, 0, H * dk, 2 * H * dk, state, dec, out, scratch, qo, pos, slots,
+                                     torch.tensor(treq, dtype=I32, device=DEV), torch.tensor(r0, dtype=I32, device=DEV),
+                                     len(r0), 2, H, dk, dv)
+            else:
+                ops.decay_attn(proj, 0, H * dk, 2 * H * dk, state, dec, out, qo, pos, slots, 2, H, dk, dv,
+                               single_rows=c == 1, multi_rows=c > 1)
             got[0].append(out[:c].cpu())
             got[1].append(out[c:].cpu())
             lo += c

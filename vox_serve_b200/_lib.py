@@ -119,10 +119,14 @@ SIGNATURES = {
                                      c_int, c_int, c_float, c_int, P]),
     "vb_decay_attn": (c_int, [P, P, P, c_int, c_int, c_int, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
                               P]),
+    "vb_decay_attn_tile_rows": (c_int, [c_int, c_int]),
+    "vb_decay_attn_tiled": (c_int, [P, P, P, P, c_int, c_int, c_int, c_int, P, P, P, P, P, P, c_int, c_int, c_int, c_int,
+                                    c_int, P]),
     "vb_gated_rmsnorm": (c_int, [P, P, P, P, c_int, c_int, c_int, c_float, c_int, P]),
     "vb_moe_route": (c_int, [P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P]),
     "vb_moe_group": (c_int, [P, P, P, P, c_int, c_int, c_int, P]),
     "vb_moe_combine": (c_int, [P, P, P, P, P, c_int, c_int, c_int, P]),
+    "vb_moe_scale_dense": (c_int, [P, P, P, c_int, c_int, c_int, c_int, c_int, P]),
 }
 
 _lock = threading.Lock()
@@ -184,7 +188,7 @@ def check(rc: int, what: str = ""):
 # kernels (+ memset nodes) each entry point enqueues; everything not listed launches exactly one
 LAUNCHES = {"vb_set_pdl": 0, "vb_set_trace": 0, "vb_weight_tiles_bytes": 0, "vb_tensor_map_kv": 0,
             "vb_tensor_map_2d_bf16": 0, "vb_device_info": 0, "vb_sample": 1, "vb_update_repetition_cache": 1,
-            "vb_set_gemm_smem_kb": 0, "vb_window_attn_tile_rows": 0}
+            "vb_set_gemm_smem_kb": 0, "vb_window_attn_tile_rows": 0, "vb_decay_attn_tile_rows": 0, "vb_decay_attn_tiled": 3}
 launch_counter = [0]
 
 

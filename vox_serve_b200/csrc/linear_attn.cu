@@ -7,6 +7,8 @@
 //                           of C tokens: scores A = (Q K^T) .* decay^(i-j) for j <= i, output O = A V + decay^(i+1) Q S,
 //                           then S <- decay^C S + sum_j decay^(C-1-j) k_j v_j^T.  Only non-negative powers of the decay
 //                           appear, so small decays underflow to zero instead of overflowing.
+//   vb_decay_attn_tiled     the same result with the portion's chunks processed in parallel (local chunk states, a scan over
+//                           them, outputs per chunk): what a long prompt runs
 //   vb_decay_attn_step      single new tokens: CTA = (request, head, block of value dims), one read and one write of the
 //                           state, the output reduced over the key dims in shared memory.
 //   vb_gated_rmsnorm        rows of concatenated heads: x / sqrt(mean(x^2) + eps) * weight * sigmoid(gate).
@@ -153,6 +155,149 @@ __global__ void __launch_bounds__(256) decay_attn_step_kernel(DecayAttnParams p)
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------------------------
+// Sequence-parallel form for prompt portions.  The portion of every request is cut into tiles of DT_ROWS consecutive rows
+// (tile i = rows tile_row0[i].. of request tile_req[i]; the tiles of a request are consecutive, requests in batch order,
+// only requests that bring two or more rows have tiles):
+//   1. per tile, in parallel:  U = sum_j decay^(L-1-j) k_j v_j^T                      -> scratch[tile][h]
+//   2. per request, in order:  scratch[tile][h] <- S before the tile;  S <- decay^L S + U;  the slot gets the final S
+//   3. per tile, in parallel:  O = (Q K^T .* decay^(i-j), j <= i) V + decay^(i+1) Q S_before
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int DT_ROWS = 64;
+
+struct DecayTileParams {
+  DecayAttnParams a;
+  float* scratch;              // [tiles][H][dim][vdim]
+  const int32_t* tile_req;
+  const int32_t* tile_row0;
+  int B;
+};
+
+__global__ void __launch_bounds__(256) decay_tile_state_kernel(DecayTileParams tp) {
+  extern __shared__ float smf[];
+  pdl_sync();
+  const DecayAttnParams& p = tp.a;
+  const int tile = blockIdx.x, h = blockIdx.y, e0 = blockIdx.z * p.dvb;
+  const int b = tp.tile_req[tile], row0 = tp.tile_row0[tile];
+  const int L = min(DT_ROWS, p.qo_indptr[b + 1] - row0);
+  const int dk = p.dim, dkp = dk + 1, DV = min(p.dvb, p.vdim - e0), dvp = p.dvb + 1;
+  float* Sk = smf;                       // [64][dk + 1]
+  float* Sv = Sk + DT_ROWS * dkp;        // [64][dvb + 1]
+  float* pw = Sv + DT_ROWS * dvp;        // [65]
+  const int tid = threadIdx.x;
+  const double d = static_cast<double>(p.decay[h]);
+  for (int i = tid; i <= DT_ROWS; i += 256) pw[i] = static_cast<float>(pow(d, static_cast<double>(i)));
+  for (int i = tid; i < L * dk; i += 256) {
+    const int r = i / dk, k = i - r * dk;
+    Sk[r * dkp + k] = silu_f(p.proj[static_cast<size_t>(row0 + r) * p.ldp + p.k_off + h * dk + k]);
+  }
+  for (int i = tid; i < L * DV; i += 256) {
+    const int r = i / DV, e = i - r * DV;
+    Sv[r * dvp + e] = silu_f(p.proj[static_cast<size_t>(row0 + r) * p.ldp + p.v_off + h * p.vdim + e0 + e]);
+  }
+  __syncthreads();
+  float* U = tp.scratch + ((static_cast<size_t>(tile) * p.H + h) * dk) * p.vdim;
+  for (int i = tid; i < dk * DV; i += 256) {
+    const int k = i / DV, e = i - k * DV;
+    float a = 0.f;
+    for (int j = 0; j < L; ++j) a = fmaf(pw[L - 1 - j] * Sk[j * dkp + k], Sv[j * dvp + e], a);
+    U[static_cast<size_t>(k) * p.vdim + e0 + e] = a;
+  }
+}
+
+__global__ void __launch_bounds__(256) decay_tile_scan_kernel(DecayTileParams tp) {
+  pdl_sync();
+  const DecayAttnParams& p = tp.a;
+  const int b = blockIdx.x, h = blockIdx.y;
+  const int r0 = p.qo_indptr[b], n = p.qo_indptr[b + 1] - r0;
+  if (n < 2) return;
+  int first = 0;                          // tiles of the requests before this one
+  for (int bb = 0; bb < b; ++bb) {
+    const int nn = p.qo_indptr[bb + 1] - p.qo_indptr[bb];
+    if (nn >= 2) first += (nn + DT_ROWS - 1) / DT_ROWS;
+  }
+  const int n_tiles = (n + DT_ROWS - 1) / DT_ROWS;
+  const bool fresh = p.pos[r0] == 0;
+  const double d = static_cast<double>(p.decay[h]);
+  const float d_full = static_cast<float>(pow(d, static_cast<double>(DT_ROWS)));
+  const float d_last = static_cast<float>(pow(d, static_cast<double>(n - (n_tiles - 1) * DT_ROWS)));
+  const size_t per = static_cast<size_t>(p.dim) * p.vdim;
+  float* S = p.state + (static_cast<size_t>(p.slots[b]) * p.H + h) * per;
+  for (size_t i = blockIdx.z * blockDim.x + threadIdx.x; i < per; i += static_cast<size_t>(gridDim.z) * blockDim.x) {
+    float s = fresh ? 0.f : S[i];
+    for (int c = 0; c < n_tiles; ++c) {
+      float* u = tp.scratch + (static_cast<size_t>(first + c) * p.H + h) * per + i;
+      const float uv = *u;
+      *u = s;
+      s = (c == n_tiles - 1 ? d_last : d_full) * s + uv;
+    }
+    S[i] = s;
+  }
+}
+
+__global__ void __launch_bounds__(256) decay_tile_out_kernel(DecayTileParams tp) {
+  extern __shared__ float smf[];
+  pdl_sync();
+  const DecayAttnParams& p = tp.a;
+  const int tile = blockIdx.x, h = blockIdx.y, e0 = blockIdx.z * p.dvb;
+  const int b = tp.tile_req[tile], row0 = tp.tile_row0[tile];
+  const int L = min(DT_ROWS, p.qo_indptr[b + 1] - row0);
+  constexpr int C = DT_ROWS;
+  const int dk = p.dim, dkp = dk + 1, DV = min(p.dvb, p.vdim - e0), dvp = p.dvb + 1;
+  float* Sq = smf;                    // [C][dk + 1]
+  float* Sk = Sq + C * dkp;           // [C][dk + 1]
+  float* Sv = Sk + C * dkp;           // [C][dvb + 1]
+  float* Sa = Sv + C * dvp;           // [C][C + 1]
+  float* Ss = Sa + C * (C + 1);       // [dk][dvb + 1]
+  float* pw = Ss + dk * dvp;          // [C + 1]
+  const int tid = threadIdx.x;
+  const double d = static_cast<double>(p.decay[h]);
+  for (int i = tid; i <= C; i += 256) pw[i] = static_cast<float>(pow(d, static_cast<double>(i)));
+  const float* Sb = tp.scratch + ((static_cast<size_t>(tile) * p.H + h) * dk) * p.vdim;
+  for (int i = tid; i < dk * DV; i += 256) {
+    const int k = i / DV, e = i - k * DV;
+    Ss[k * dvp + e] = Sb[static_cast<size_t>(k) * p.vdim + e0 + e];
+  }
+  for (int i = tid; i < C * dk; i += 256) {
+    const int r = i / dk, k = i - r * dk;
+    float qv = 0.f, kv = 0.f;
+    if (r < L) {
+      const float* row = p.proj + static_cast<size_t>(row0 + r) * p.ldp + h * dk + k;
+      qv = silu_f(row[p.q_off]);
+      kv = silu_f(row[p.k_off]);
+    }
+    Sq[r * dkp + k] = qv;
+    Sk[r * dkp + k] = kv;
+  }
+  for (int i = tid; i < C * DV; i += 256) {
+    const int r = i / DV, e = i - r * DV;
+    Sv[r * dvp + e] = r < L ? silu_f(p.proj[static_cast<size_t>(row0 + r) * p.ldp + p.v_off + h * p.vdim + e0 + e]) : 0.f;
+  }
+  __syncthreads();
+  for (int i = tid; i < C * C; i += 256) {
+    const int r = i / C, j = i - r * C;
+    float a = 0.f;
+    if (j <= r && r < L) {
+      const float* qr = Sq + r * dkp;
+      const float* kr = Sk + j * dkp;
+      for (int k = 0; k < dk; ++k) a = fmaf(qr[k], kr[k], a);
+      a *= pw[r - j];
+    }
+    Sa[r * (C + 1) + j] = a;
+  }
+  __syncthreads();
+  for (int i = tid; i < L * DV; i += 256) {
+    const int r = i / DV, e = i - r * DV;
+    float intra = 0.f, inter = 0.f;
+    const float* ar = Sa + r * (C + 1);
+    for (int j = 0; j <= r; ++j) intra = fmaf(ar[j], Sv[j * dvp + e], intra);
+    const float* qr = Sq + r * dkp;
+    for (int k = 0; k < dk; ++k) inter = fmaf(qr[k], Ss[k * dvp + e], inter);
+    p.out[static_cast<size_t>(row0 + r) * p.H * p.vdim + h * p.vdim + e0 + e] = intra + pw[r + 1] * inter;
+  }
+}
+
 template <typename OT>
 __global__ void gated_rmsnorm_kernel(OT* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w,
                                      const float* __restrict__ gate, int ld_gate, int N, float eps) {
@@ -186,6 +331,12 @@ static size_t chunked_smem(int C, int dk, int dvb) {
           static_cast<size_t>(dk) * (dvb + 1) + C + 1) * sizeof(float);
 }
 
+static int decay_dvb(int vdim) {
+  int dvb = 64;
+  while (dvb > 1 && dvb / 2 >= vdim) dvb /= 2;       // the smallest power of two >= vdim, at most 64
+  return dvb;
+}
+
 }  // namespace vb
 
 using namespace vb;
@@ -198,8 +349,7 @@ int vb_decay_attn(float* d_out, float* d_state, const float* d_proj, int ldp, in
   VB_CHECK_ARG(d_out && d_state && d_proj && d_decay && d_qo_indptr && d_pos && d_slots, "vb_decay_attn: null pointer");
   VB_CHECK_ARG(H > 0 && dim > 0 && vdim > 0, "vb_decay_attn: bad sizes H=%d dim=%d vdim=%d", H, dim, vdim);
   if (B <= 0) return 0;
-  int dvb = 64;
-  while (dvb > 1 && dvb / 2 >= vdim) dvb /= 2;       // the smallest power of two >= vdim, at most 64
+  const int dvb = decay_dvb(vdim);
   DecayAttnParams p{d_proj, ldp, q_off, k_off, v_off, d_out, d_state, d_decay, d_qo_indptr, d_pos, d_slots,
                     H, dim, vdim, dvb, 0, 0, 0};
   dim3 grid(B, H, (vdim + dvb - 1) / dvb);
@@ -221,6 +371,34 @@ int vb_decay_attn(float* d_out, float* d_state, const float* d_proj, int ldp, in
     VB_CHECK_CUDA(cudaFuncSetAttribute(decay_attn_chunked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
     VB_LAUNCH_PDL(decay_attn_chunked_kernel, grid, 256, smem, stream, p);
   }
+  return 0;
+}
+
+/* rows per tile of the sequence-parallel form, or 0 when these head sizes do not fit its shared memory */
+int vb_decay_attn_tile_rows(int dim, int vdim) {
+  return chunked_smem(DT_ROWS, dim, decay_dvb(vdim)) <= static_cast<size_t>(VB_MAX_DYN_SMEM) ? DT_ROWS : 0;
+}
+
+int vb_decay_attn_tiled(float* d_out, float* d_state, float* d_scratch, const float* d_proj, int ldp, int q_off, int k_off,
+                        int v_off, const float* d_decay, const int32_t* d_qo_indptr, const int32_t* d_pos,
+                        const int32_t* d_slots, const int32_t* d_tile_req, const int32_t* d_tile_row0, int n_tiles, int B,
+                        int H, int dim, int vdim, void* stream) {
+  VB_CHECK_ARG(d_out && d_state && d_scratch && d_proj && d_decay && d_qo_indptr && d_pos && d_slots && d_tile_req &&
+               d_tile_row0, "vb_decay_attn_tiled: null pointer");
+  VB_CHECK_ARG(H > 0 && dim > 0 && vdim > 0 && vb_decay_attn_tile_rows(dim, vdim) > 0, "vb_decay_attn_tiled: bad sizes");
+  if (n_tiles <= 0 || B <= 0) return 0;
+  const int dvb = decay_dvb(vdim);
+  DecayTileParams tp{{d_proj, ldp, q_off, k_off, v_off, d_out, d_state, d_decay, d_qo_indptr, d_pos, d_slots, H, dim, vdim,
+                      dvb, DT_ROWS, 2, 1 << 30}, d_scratch, d_tile_req, d_tile_row0, B};
+  const int zb = (vdim + dvb - 1) / dvb;
+  const size_t smem1 = (static_cast<size_t>(DT_ROWS) * (dim + 1 + dvb + 1) + DT_ROWS + 1) * sizeof(float);
+  const size_t smem3 = chunked_smem(DT_ROWS, dim, dvb);
+  VB_CHECK_CUDA(cudaFuncSetAttribute(decay_tile_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+  VB_CHECK_CUDA(cudaFuncSetAttribute(decay_tile_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+  VB_LAUNCH_PDL(decay_tile_state_kernel, dim3(n_tiles, H, zb), 256, smem1, stream, tp);
+  const size_t per = static_cast<size_t>(dim) * vdim;
+  VB_LAUNCH_PDL(decay_tile_scan_kernel, dim3(B, H, static_cast<unsigned>((per + 1023) / 1024)), 256, 0, stream, tp);
+  VB_LAUNCH_PDL(decay_tile_out_kernel, dim3(n_tiles, H, zb), 256, smem3, stream, tp);
   return 0;
 }
 

@@ -4,6 +4,12 @@
 //                   expert index), weights = softmax over the chosen logits only
 //   vb_moe_group    counting sort of the (token, choice) pairs by expert: row_off[E + 1], the token of every sorted row and
 //                   the sorted row of every (token, choice)
+//   vb_moe_scale_dense  the dense form for tensor-core projections: every expert runs on every token as ONE stacked
+//                   gate/up projection [E * ff (+ shared ff)] and ONE stacked down projection over that whole axis; in
+//                   between, the activation columns of expert e are multiplied by the token's routing weight for e, or
+//                   set to zero when e was not chosen (the shared expert's columns pass).  Weight-bound steps (decode)
+//                   read every expert's matrices once either way; compute-bound steps pay experts / top times the FLOPs
+//                   of the grouped form, on tensor cores instead of fp32 FMAs.
 //   vb_moe_combine  y[t] = sum_c weight[t][c] * expert_out[sorted row of (t, c)] (+ shared[t]), summed in choice order so
 //                   that a token's result does not depend on what else is in the batch
 #include "../../include/vb_api.h"
@@ -110,6 +116,23 @@ __global__ void moe_combine_kernel(float* __restrict__ y, const float* __restric
   }
 }
 
+__global__ void moe_scale_dense_kernel(__nv_bfloat16* __restrict__ act, const int32_t* __restrict__ idx,
+                                       const float* __restrict__ wts, int ld, int E, int ff, int top) {
+  extern __shared__ float we[];     // [E] routing weight of every expert for this token (0: not chosen)
+  pdl_sync();
+  const size_t t = blockIdx.x;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) we[e] = 0.f;
+  __syncthreads();
+  if (threadIdx.x < top) we[idx[t * top + threadIdx.x]] = wts[t * top + threadIdx.x];
+  __syncthreads();
+  __nv_bfloat16* row = act + t * ld;
+  const int n = E * ff;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    const float w = we[c / ff];
+    row[c] = w == 0.f ? __float2bfloat16_rn(0.f) : __float2bfloat16_rn(w * __bfloat162float(row[c]));
+  }
+}
+
 }  // namespace vb
 
 using namespace vb;
@@ -134,6 +157,16 @@ int vb_moe_group(int32_t* d_row_off, int32_t* d_sorted_token, int32_t* d_pair_ro
   VB_CHECK_ARG(experts >= 1 && experts <= 1024, "vb_moe_group: experts %d (<= 1024)", experts);
   if (T <= 0) return 0;
   VB_LAUNCH_PDL(moe_group_kernel, 1, 1024, 0, stream, d_row_off, d_sorted_token, d_pair_row, d_idx, T, experts, top);
+  return 0;
+}
+
+int vb_moe_scale_dense(void* d_act, const int32_t* d_idx, const float* d_wts, int T, int ld, int experts, int ff, int top,
+                       void* stream) {
+  VB_CHECK_ARG(d_act && d_idx && d_wts, "vb_moe_scale_dense: null pointer");
+  VB_CHECK_ARG(experts >= 1 && experts <= 1024 && top >= 1 && top <= 32 && ld >= experts * ff, "vb_moe_scale_dense: bad sizes");
+  if (T <= 0) return 0;
+  VB_LAUNCH_PDL(moe_scale_dense_kernel, T, 256, static_cast<size_t>(experts) * sizeof(float), stream,
+                static_cast<__nv_bfloat16*>(d_act), d_idx, d_wts, ld, experts, ff, top);
   return 0;
 }
 

@@ -6,9 +6,9 @@
 //                        every layer of a step that has the same rotary constants)
 //   vb_qkv_rotary_append the tail of a fused q|k|v|gate projection: rotate q and k, mix v with the first mixing layer's
 //                        values of the same token, write q, append k and the mixed v to the layer's pages
-//   vb_window_attn       one warp per (token row, query head): keys lo..pos of the row's request in chunks of 32 (one
-//                        key per lane for the scores, one slice of the value head per lane for the output), online
-//                        softmax, gate, store.  Serves decode rows and prompt portions alike.
+//   vb_window_attn       decode rows (and steps that mix them with prompt portions): a CTA per (token row, key/value
+//                        head) whose K / V tiles serve all query heads of the group; for head groups or value sizes
+//                        beyond its registers, one warp per (token row, query head).  Online softmax, gate, store.
 //   vb_window_attn_tiled prompt portions: one CTA per (64 query rows of one request, query head), K/V tiles staged in
 //                        shared memory and reused by all rows of the tile.
 // Cache layout per layer: K [pages][page_size][kv_heads][dim], V [pages][page_size][kv_heads][vdim].
@@ -333,6 +333,115 @@ __global__ void __launch_bounds__(256) window_attn_tiled_kernel(WindowAttnParams
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// Decode rows: CTA = (token row, key/value head), 128 threads.  All R = H / G query heads of the group share every K / V
+// tile of 32 positions, staged once in shared memory as fp32 with coalesced loads.  Warp w owns the heads r = w, w + 4, ..:
+// lane j scores key j of the tile for them, the softmax statistics of a head stay inside its warp, and in the output phase
+// lane d accumulates value dims d, d + 32, .. of the same heads.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int WD_KEYS = 32, WD_RU = 4, WD_VU = 8;      // up to 4 * WD_RU query heads per key/value head, vdim <= 32 * WD_VU
+
+template <typename CT>
+__global__ void __launch_bounds__(128) window_attn_group_kernel(WindowAttnParams p) {
+  extern __shared__ float smf[];
+  pdl_sync();
+  const int t = blockIdx.x, g = blockIdx.y, R = p.H / p.G;
+  const int dk = p.dim, dv = p.vdim, dkp = dk + 1, dvp = dv + 1;
+  float* Qs = smf;                      // [R][dk]
+  float* Ks = Qs + R * dk;              // [32][dk + 1]
+  float* Vs = Ks + WD_KEYS * dkp;       // [32][dv + 1]
+  float* Ps = Vs + WD_KEYS * dvp;       // [R][32]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const CT* q = static_cast<const CT*>(p.q) + (static_cast<size_t>(t) * p.H + g * R) * dk;
+  for (int i = tid; i < R * dk; i += 128) Qs[i] = wa_to_f(q[i]) * p.scale;
+  const int b = p.row_req[t], ps = p.pos[t];
+  const int32_t* pages = p.page_indices + p.page_indptr[b];
+  const int lo = p.window > 0 ? max(0, ps - p.window + 1) : 0;
+  const CT* kc = static_cast<const CT*>(p.k_cache);
+  const CT* vc = static_cast<const CT*>(p.v_cache);
+  float m[WD_RU], l[WD_RU], acc[WD_RU][WD_VU];
+#pragma unroll
+  for (int u = 0; u < WD_RU; ++u) {
+    m[u] = -INFINITY;
+    l[u] = 0.f;
+#pragma unroll
+    for (int v = 0; v < WD_VU; ++v) acc[u][v] = 0.f;
+  }
+  for (int c0 = lo; c0 <= ps; c0 += WD_KEYS) {
+    __syncthreads();
+    const int nk = min(WD_KEYS, ps - c0 + 1);
+    for (int i = tid; i < WD_KEYS * dk; i += 128) {
+      const int kk = i / dk, d = i - kk * dk;
+      float v = 0.f;
+      if (kk < nk) {
+        const int kj = c0 + kk;
+        const size_t tok = static_cast<size_t>(pages[kj / p.page_size]) * p.page_size + kj % p.page_size;
+        v = wa_to_f(kc[(tok * p.G + g) * dk + d]);
+      }
+      Ks[kk * dkp + d] = v;
+    }
+    for (int i = tid; i < WD_KEYS * dv; i += 128) {
+      const int kk = i / dv, d = i - kk * dv;
+      float v = 0.f;
+      if (kk < nk) {
+        const int kj = c0 + kk;
+        const size_t tok = static_cast<size_t>(pages[kj / p.page_size]) * p.page_size + kj % p.page_size;
+        v = wa_to_f(vc[(tok * p.G + g) * dv + d]);
+      }
+      Vs[kk * dvp + d] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int u = 0; u < WD_RU; ++u) {
+      const int r = warp + 4 * u;
+      if (r >= R) break;
+      float s = -INFINITY;
+      if (lane < nk) {
+        const float* qr = Qs + r * dk;
+        const float* kr = Ks + lane * dkp;
+        float a = 0.f;
+        for (int d = 0; d < dk; ++d) a = fmaf(qr[d], kr[d], a);
+        s = a;
+      }
+      const float m_new = fmaxf(m[u], warp_max(s));
+      const float corr = expf(m[u] - m_new);
+      const float pj = lane < nk ? expf(s - m_new) : 0.f;
+      l[u] = l[u] * corr + warp_sum(pj);
+      m[u] = m_new;
+      Ps[r * WD_KEYS + lane] = pj;
+      __syncwarp();
+      const float* pr = Ps + r * WD_KEYS;
+#pragma unroll
+      for (int v = 0; v < WD_VU; ++v) {
+        const int d = lane + 32 * v;
+        if (d < dv) {
+          float a = acc[u][v] * corr;
+          for (int kk = 0; kk < nk; ++kk) a = fmaf(pr[kk], Vs[kk * dvp + d], a);
+          acc[u][v] = a;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < WD_RU; ++u) {
+    const int r = warp + 4 * u;
+    if (r >= R) break;
+    const int h = g * R + r;
+    const float inv = 1.f / l[u];
+    CT* out = static_cast<CT*>(p.out) + static_cast<size_t>(t) * p.H * dv + h * dv;
+    const float* gate = p.gate ? p.gate + static_cast<size_t>(t) * p.ld_gate + h * dv : nullptr;
+#pragma unroll
+    for (int v = 0; v < WD_VU; ++v) {
+      const int d = lane + 32 * v;
+      if (d < dv) {
+        float o = acc[u][v] * inv;
+        if (gate) o *= 1.f / (1.f + expf(-gate[d]));
+        out[d] = wa_from_f<CT>(o);
+      }
+    }
+  }
+}
+
 }  // namespace vb
 
 using namespace vb;
@@ -376,6 +485,22 @@ int vb_window_attn(void* d_out, const void* d_q, const void* d_k_cache, const vo
   if (T <= 0) return 0;
   WindowAttnParams p{d_q, d_k_cache, d_v_cache, d_out, d_gate, ld_gate, d_row_req, d_pos, d_page_indptr, d_page_indices,
                      nullptr, nullptr, nullptr, T, H, G, dim, vdim, page_size, window, scale};
+  // a CTA per (row, key/value head) with the K / V tiles shared by the group's query heads, when the group fits its
+  // registers and the tiles fit shared memory; one warp per (row, query head) otherwise
+  const int R = H / G;
+  const size_t gsmem = (static_cast<size_t>(R) * dim + static_cast<size_t>(WD_KEYS) * (dim + 1 + vdim + 1) +
+                        static_cast<size_t>(R) * WD_KEYS) * sizeof(float);
+  if (R <= 4 * WD_RU && vdim <= 32 * WD_VU && gsmem <= 96 * 1024) {
+    dim3 ggrid(T, G);
+    if (dtype == 1) {
+      VB_CHECK_CUDA(cudaFuncSetAttribute(window_attn_group_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+      VB_LAUNCH_PDL(window_attn_group_kernel<float>, ggrid, 128, gsmem, stream, p);
+    } else {
+      VB_CHECK_CUDA(cudaFuncSetAttribute(window_attn_group_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+      VB_LAUNCH_PDL(window_attn_group_kernel<bf16>, ggrid, 128, gsmem, stream, p);
+    }
+    return 0;
+  }
   const size_t smem = static_cast<size_t>(WA_WARPS) * dim * sizeof(float);
   VB_CHECK_ARG(smem <= 48 * 1024, "vb_window_attn: head dim %d too large", dim);
   dim3 grid((T + WA_WARPS - 1) / WA_WARPS, H);

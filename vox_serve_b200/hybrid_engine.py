@@ -219,12 +219,26 @@ class HybridWeights:
                 w["norm2"], w["norm2b"] = norm(p + "norm2"), norm(p + "norm2b")
                 w["router"] = vec(p + "mlp.router")
                 w["router_b"] = vec(p + "mlp.router.b") if (p + "mlp.router.b") in sd else None
-                w["gu"] = torch.stack([mat(p + f"mlp.e{e}.gate", p + f"mlp.e{e}.up") for e in range(f.experts)]).contiguous()
-                w["down"] = torch.stack([mat(p + f"mlp.e{e}.down") for e in range(f.experts)]).contiguous()
-                if f.shared_ff:
-                    w["s_gu"] = gate_up(p + "mlp.shared.gate", p + "mlp.shared.up")
-                    w["s_down"] = dense(mat(p + "mlp.shared.down"))
+                n_all = f.experts * f.ff + f.shared_ff
+                if self.tensor_core and cfg.width % 8 == 0 and n_all % 8 == 0 and f.experts <= self.DENSE_MOE_MAX_RATIO * f.top:
+                    # dense form (vb_moe_scale_dense): all experts and the shared expert as one gate/up and one down matrix
+                    names = [f"e{e}" for e in range(f.experts)] + (["shared"] if f.shared_ff else [])
+                    gate = torch.cat([mat(p + f"mlp.{n}.gate") for n in names], 0)
+                    up = torch.cat([mat(p + f"mlp.{n}.up") for n in names], 0)
+                    half = ops.gate_up_tile_half(n_all)
+                    w["gu_all"] = ops.pack_weight(ops.interleave_gate_up(gate, up, half), 2 * half)
+                    del gate, up
+                    w["down_all"] = ops.pack_weight(torch.cat([mat(p + f"mlp.{n}.down") for n in names], 1).contiguous(), 128)
+                else:
+                    w["gu"] = torch.stack([mat(p + f"mlp.e{e}.gate", p + f"mlp.e{e}.up") for e in range(f.experts)]).contiguous()
+                    w["down"] = torch.stack([mat(p + f"mlp.e{e}.down") for e in range(f.experts)]).contiguous()
+                    if f.shared_ff:
+                        w["s_gu"] = gate_up(p + "mlp.shared.gate", p + "mlp.shared.up")
+                        w["s_down"] = dense(mat(p + "mlp.shared.down"))
             self.layers.append(w)
+
+    # the dense mixture-of-experts form runs experts / top times the FLOPs a token needs: taken up to this ratio
+    DENSE_MOE_MAX_RATIO = 8
 
     def nbytes(self) -> int:
         n = 0
@@ -313,6 +327,14 @@ class HybridEngine:
         self.q = torch.zeros(R * max([m.heads * m.dim for m in att] + [1]), dtype=CT, device=dev)
         self.mix_out = torch.zeros(R * hv, dtype=CT, device=dev)       # gated mixer output, input of the o projection
         self.lin_o = torch.zeros(R * hv, dtype=F32, device=dev)        # linear-attention output before its norm
+        # scratch of the sequence-parallel linear attention: one state per tile of 64 rows (a step has at most
+        # max_rows / 64 full tiles plus one partial tile per request)
+        self.lin_tile_rows = ops.window_attn_tile_rows() if dev.type == "cuda" else 64
+        self.lin_scratch = None
+        tiled = [m for m in lin if ops.decay_attn_tile_rows(m.dim, m.vdim) == self.lin_tile_rows] if dev.type == "cuda" else []
+        if tiled:
+            n_t = max_rows // self.lin_tile_rows + max_out_rows + 1
+            self.lin_scratch = torch.zeros(n_t * max(m.heads * m.dim * m.vdim for m in tiled), dtype=F32, device=dev)
         self.v_first = torch.zeros(R * max([m.kv_heads * m.vdim for m in att if m.v_mix] + [1]), dtype=F32, device=dev)
         self.freqs: Dict[Tuple, torch.Tensor] = {}
         self.cs: Dict[Tuple, torch.Tensor] = {}
@@ -329,7 +351,8 @@ class HybridEngine:
             self.moe_row_off = torch.zeros(E + 1, dtype=I32, device=dev)
             self.moe_sorted = torch.zeros(R * top, dtype=I32, device=dev)
             self.moe_pair_row = torch.zeros(R * top, dtype=I32, device=dev)
-            self.moe_act = torch.zeros(R * max(f.top * f.ff for f in moe), dtype=CT, device=dev)
+            self.moe_act = torch.zeros(R * max(max(f.top * f.ff, f.experts * f.ff + f.shared_ff) for f in moe), dtype=CT,
+                                       device=dev)
             self.moe_out = torch.zeros(R * top * W, dtype=F32, device=dev)
             self.s_act = torch.zeros(R * max([f.shared_ff for f in moe] + [1]), dtype=CT, device=dev)
             self.s_out = torch.zeros(R, W, dtype=F32, device=dev)
@@ -382,8 +405,15 @@ class HybridEngine:
         P = 2 * nq + 2 * nv
         proj = self._proj(self.h[:T], w["qkvg"], self.proj[:T * P].view(T, P))
         o = self.lin_o[:T * nv].view(T, nv)
-        ops.decay_attn(proj, 0, nq, 2 * nq, self.cache.state[i], w["decay"], o, s.qo_indptr, s.pos, s.slots, s.B, m.heads,
-                       m.dim, m.vdim, single_rows=s.single, multi_rows=s.multi)
+        par = (s.multi and s.tiles is not None and self.lin_scratch is not None
+               and ops.decay_attn_tile_rows(m.dim, m.vdim) == self.lin_tile_rows
+               and s.tiles[2] * m.heads * m.dim * m.vdim <= self.lin_scratch.numel())
+        if s.single or (s.multi and not par):
+            ops.decay_attn(proj, 0, nq, 2 * nq, self.cache.state[i], w["decay"], o, s.qo_indptr, s.pos, s.slots, s.B, m.heads,
+                           m.dim, m.vdim, single_rows=s.single, multi_rows=s.multi and not par)
+        if par:
+            ops.decay_attn_tiled(proj, 0, nq, 2 * nq, self.cache.state[i], w["decay"], o, self.lin_scratch, s.qo_indptr, s.pos,
+                                 s.slots, s.tiles[0], s.tiles[1], s.tiles[2], s.B, m.heads, m.dim, m.vdim)
         out = self.mix_out[:T * nv].view(T, nv)
         ops.gated_rmsnorm(o, w["norm"], proj[:, 2 * nq + nv:], self.cfg.eps, out)
         self._proj(out, w["o"], self.y[:T])
@@ -393,6 +423,13 @@ class HybridEngine:
         h = self.h[:T]
         idx, wts = self.moe_idx[:T * f.top], self.moe_wts[:T * f.top]
         ops.moe_route(h, w["router"], w["router_b"], f.top, idx, wts)
+        if "gu_all" in w:
+            n_all = f.experts * f.ff + f.shared_ff
+            act = self.moe_act[:T * n_all].view(T, n_all)
+            ops.gemm(h, w["gu_all"], mode=2, out=act, tile_rows=w["gu_all"].tile_rows, n_out=n_all)
+            ops.moe_scale_dense(act, idx, wts, f.experts, f.ff, f.top)
+            self._proj(act, w["down_all"], self.y[:T])
+            return
         ops.moe_group(idx, T, f.experts, f.top, self.moe_row_off, self.moe_sorted, self.moe_pair_row)
         act = self.moe_act[:T * f.top * f.ff].view(T * f.top, f.ff)
         ops.linear(h, w["gu"], act, epilogue=1, row_off=self.moe_row_off, gather=self.moe_sorted, rows=T)

@@ -1036,6 +1036,24 @@ def decay_attn(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, state: to
     return out
 
 
+def decay_attn_tile_rows(dim: int, vdim: int) -> int:
+    """Rows per tile of the sequence-parallel form (0: these head sizes only run the sequential form)."""
+    return _lib.load().vb_decay_attn_tile_rows(int(dim), int(vdim))
+
+
+def decay_attn_tiled(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, state: torch.Tensor, decay: torch.Tensor,
+                     out: torch.Tensor, scratch: torch.Tensor, qo_indptr: torch.Tensor, pos: torch.Tensor,
+                     slots: torch.Tensor, tile_req: torch.Tensor, tile_row0: torch.Tensor, n_tiles: int, B: int, H: int,
+                     dim: int, vdim: int) -> torch.Tensor:
+    """Prompt portions with their tiles processed in parallel (the requests that bring one row are not touched)."""
+    _need_cuda(proj, state, decay, out, scratch)
+    assert proj.dtype == F32 and state.dtype == F32 and scratch.dtype == F32 and scratch.numel() >= n_tiles * H * dim * vdim
+    call("vb_decay_attn_tiled", out.data_ptr(), state.data_ptr(), scratch.data_ptr(), proj.data_ptr(), proj.stride(0), q_off,
+         k_off, v_off, decay.data_ptr(), qo_indptr.data_ptr(), pos.data_ptr(), slots.data_ptr(), tile_req.data_ptr(),
+         tile_row0.data_ptr(), n_tiles, B, H, dim, vdim, _stream())
+    return out
+
+
 def gated_rmsnorm(x: torch.Tensor, w: torch.Tensor, gate: Optional[torch.Tensor], eps: float, out: torch.Tensor):
     """out = x / sqrt(mean(x^2) + eps) * w * sigmoid(gate); x, w, gate fp32 (gate: a view with any row stride)."""
     _need_cuda(x, w, out)
@@ -1066,3 +1084,12 @@ def moe_combine(expert_out: torch.Tensor, shared_out: Optional[torch.Tensor], wt
     call("vb_moe_combine", out.data_ptr(), expert_out.data_ptr(), _p(shared_out), wts.data_ptr(), pair_row.data_ptr(),
          out.shape[0], out.shape[1], top, _stream())
     return out
+
+
+def moe_scale_dense(act: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, experts: int, ff: int, top: int) -> torch.Tensor:
+    """act bf16 [T, >= experts * ff] in place: columns of expert e times the token's routing weight for e (0 if not chosen)."""
+    _need_cuda(act, idx, wts)
+    assert act.dtype == BF16 and act.stride(1) == 1
+    call("vb_moe_scale_dense", act.data_ptr(), idx.data_ptr(), wts.data_ptr(), act.shape[0], act.stride(0), experts, ff, top,
+         _stream())
+    return act
