@@ -484,6 +484,8 @@ int vb_linear(void* d_out, const void* d_x, const void* d_w, int T, int N, int K
               int out_dtype, int epilogue, float alpha, const int32_t* d_row_off, const int32_t* d_gather, int groups,
               long long w_group_stride, void* stream);
 int vb_cast_f32_bf16(void* d_out, const float* d_in, long long n, void* stream);
+/* out[i] = sum_s partials[s * n + i], s < planes, in plane order (fp32 partial planes of a split-K projection) */
+int vb_sum_planes_f32(float* d_out, const float* d_partials, int planes, long long n, void* stream);
 /* Sliding-window attention over per-layer pages K [pages][page][G][dim], V [pages][page][G][vdim].
  * vb_rotary_table:      cs[t] = cos | sin of pos[t] * freq[j], j < half (freq in double)
  * vb_qkv_rotary_append: from the fp32 projection rows [T][ldp] (q at q_off, k at k_off, v at v_off): rotate the first

@@ -137,7 +137,7 @@ def _err(got, ref):
     return e.max().item()
 
 
-TOL = {F32: 2e-4, BF16: 6e-2}
+TOL = {F32: 2e-4, BF16: 8e-2}
 
 
 def _tokens(n, vocab, seed):
@@ -203,7 +203,7 @@ def test_other_sizes():
 def test_prefill_decode_portions_and_batches(dtype):
     """the same logits whether a sequence runs whole, token by token, in portions of changing size (down to two tokens,
     cut inside pages, windows and chunks) or in batches with other requests; pages and slots are used again."""
-    cfg = O.make_config(layers=("attention", "lightning", "attention"), window=11)
+    cfg = O.make_config(layers=("attention", "lightning", "attention"), window=11, dim=16, vdim=16)
     sd = O.random_weights(cfg, 4)
     seqs = {"a": _tokens(150, cfg["vocab"], 1), "b": _tokens(37, cfg["vocab"], 2), "c": _tokens(70, cfg["vocab"], 3),
             "d": _tokens(9, cfg["vocab"], 4), "e": _tokens(64, cfg["vocab"], 5)}
@@ -239,6 +239,7 @@ def test_long_decoding_past_window_and_pages():
 
 # ---- mechanisms with inputs that make one key stand out ---------------------------------------------------------------
 def _attention_case(window, n_tokens, page_size, hot, dtype, tiled, H=2, G=1, dk=8, dv=4):
+    # (dk = 8, dv = 4: the fp32-FMA kernels; multiples of 16 in bfloat16 with tiles: the tensor-core kernel)
     """One request of n_tokens positions.  Key `hot` gets a huge score from every query and a value of 1000 in dim 0; all
     other values are small.  Returns the attention output [T, H, dv] (no gate)."""
     from vox_serve_b200 import ops
@@ -286,12 +287,18 @@ def test_window_edges_large_head_group():
     _window_edges(False, F32, 20, 1)
 
 
-def _window_edges(tiled, dtype, H, G):
+@pytest.mark.gpu
+def test_window_edges_tensor_core_tiles():
+    _window_edges(True, BF16, 4, 2, dk=32, dv=16)
+    _window_edges(True, BF16, 2, 2, dk=128, dv=128)
+
+
+def _window_edges(tiled, dtype, H, G, dk=8, dv=4):
     """the hot key dominates exactly the queries whose window holds it: visible at distance window - 1, gone at distance
     window; with no window it is seen from hundreds of positions away, across page borders."""
     tol = 1e-3 if dtype == F32 else 3e-2
     for window, hot, T, ps in ((16, 5, 70, 8), (33, 31, 130, 16), (0, 3, 300, 8), (64, 64, 200, 64), (1, 7, 20, 4)):
-        got, ref = _attention_case(window, T, ps, hot, dtype, tiled, H=H, G=G)
+        got, ref = _attention_case(window, T, ps, hot, dtype, tiled, H=H, G=G, dk=dk, dv=dv)
         assert torch.allclose(got.double(), ref, rtol=tol, atol=tol * 10), (window, hot)
         sees = got[:, 0, 0] > 500
         for i in range(T):

@@ -109,6 +109,7 @@ SIGNATURES = {
     "vb_linear": (c_int, [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, P, P, c_int,
                           C.c_longlong, P]),
     "vb_cast_f32_bf16": (c_int, [P, P, C.c_longlong, P]),
+    "vb_sum_planes_f32": (c_int, [P, P, c_int, C.c_longlong, P]),
     "vb_rotary_table": (c_int, [P, P, P, c_int, c_int, P]),
     "vb_qkv_rotary_append": (c_int, [P, c_int, c_int, c_int, c_int, P, c_int, P, P, P, P, P, P, P, c_int, c_int, c_int,
                                      c_int, c_int, c_int, c_int, P, P, c_int, P]),

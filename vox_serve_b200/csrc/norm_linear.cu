@@ -224,6 +224,27 @@ __global__ void cast_f32_bf16_kernel(__nv_bfloat16* __restrict__ out, const floa
   if (i < n) out[i] = __float2bfloat16_rn(in[i]);
 }
 
+// out[i] = sum over planes of partials[plane][i] in plane order (the reduction of a split-K projection)
+__global__ void sum_planes_kernel(float* __restrict__ out, const float* __restrict__ partials, int planes, long long n) {
+  pdl_sync();
+  const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+  if (i >= n) return;
+  if (i + 3 < n) {
+    float4 a = *reinterpret_cast<const float4*>(partials + i);
+    for (int s = 1; s < planes; ++s) {
+      const float4 b = *reinterpret_cast<const float4*>(partials + s * n + i);
+      a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+    }
+    *reinterpret_cast<float4*>(out + i) = a;
+  } else {
+    for (long long j = i; j < n; ++j) {
+      float a = partials[j];
+      for (int s = 1; s < planes; ++s) a += partials[s * n + j];
+      out[j] = a;
+    }
+  }
+}
+
 }  // namespace vb
 
 using namespace vb;
@@ -286,6 +307,13 @@ int vb_linear(void* d_out, const void* d_x, const void* d_w, int T, int N, int K
   // in_dtype: 0 = bf16 activations and weights, 1 = fp32 both; out_dtype likewise
   if (in_dtype == 1) return out_dtype == 1 ? launch_linear<float, float, float>(p, groups, T, s) : launch_linear<float, float, bf16>(p, groups, T, s);
   return out_dtype == 1 ? launch_linear<bf16, bf16, float>(p, groups, T, s) : launch_linear<bf16, bf16, bf16>(p, groups, T, s);
+}
+
+int vb_sum_planes_f32(float* d_out, const float* d_partials, int planes, long long n, void* stream) {
+  VB_CHECK_ARG(d_out && d_partials && planes >= 1 && n % 4 == 0, "vb_sum_planes_f32: bad arguments (n a multiple of 4)");
+  if (n <= 0) return 0;
+  VB_LAUNCH_PDL(sum_planes_kernel, static_cast<unsigned>((n / 4 + 255) / 256), 256, 0, stream, d_out, d_partials, planes, n);
+  return 0;
 }
 
 int vb_cast_f32_bf16(void* d_out, const float* d_in, long long n, void* stream) {

@@ -10,7 +10,8 @@
 //                        head) whose K / V tiles serve all query heads of the group; for head groups or value sizes
 //                        beyond its registers, one warp per (token row, query head).  Online softmax, gate, store.
 //   vb_window_attn_tiled prompt portions: one CTA per (64 query rows of one request, query head), K/V tiles staged in
-//                        shared memory and reused by all rows of the tile.
+//                        shared memory and reused by all rows of the tile: mma.sync tensor-core tiles for bf16 heads whose
+//                        sizes are multiples of 16 up to 128, fp32 FMAs otherwise (and always in fp32 mode).
 // Cache layout per layer: K [pages][page_size][kv_heads][dim], V [pages][page_size][kv_heads][vdim].
 #include "../../include/vb_api.h"
 #define VB_PDL_FAMILY 1
@@ -149,6 +150,47 @@ __device__ __forceinline__ float dot_row<__nv_bfloat16>(const float* __restrict_
   return s;
 }
 
+// rows c0 .. c0 + n_rows - 1 of one key/value head of a request's pages -> dst[row][ldd] as fp32; rows at or past `valid`
+// are zero.  16-byte loads when the head size allows (8 bf16 / 4 fp32 per load), element loads otherwise.
+template <typename CT>
+__device__ __forceinline__ void load_rows_f32(float* __restrict__ dst, int ldd, const CT* __restrict__ cache,
+                                              const int32_t* __restrict__ pages, int page_size, int G, int g, int d_head,
+                                              int c0, int n_rows, int valid, int tid, int nthreads) {
+  constexpr int VEC = 16 / sizeof(CT);
+  if (d_head % VEC == 0) {
+    const int nvec = d_head / VEC;
+    for (int i = tid; i < n_rows * nvec; i += nthreads) {
+      const int kk = i / nvec, d = (i - kk * nvec) * VEC;
+      float* o = dst + kk * ldd + d;
+      if (kk < valid) {
+        const int kj = c0 + kk;
+        const size_t tok = static_cast<size_t>(pages[kj / page_size]) * page_size + kj % page_size;
+        const uint4 v = *reinterpret_cast<const uint4*>(cache + (tok * G + g) * d_head + d);
+        if constexpr (sizeof(CT) == 2) {
+          o[0] = bf16_lo(v.x); o[1] = bf16_hi(v.x); o[2] = bf16_lo(v.y); o[3] = bf16_hi(v.y);
+          o[4] = bf16_lo(v.z); o[5] = bf16_hi(v.z); o[6] = bf16_lo(v.w); o[7] = bf16_hi(v.w);
+        } else {
+          o[0] = __uint_as_float(v.x); o[1] = __uint_as_float(v.y); o[2] = __uint_as_float(v.z); o[3] = __uint_as_float(v.w);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) o[e] = 0.f;
+      }
+    }
+  } else {
+    for (int i = tid; i < n_rows * d_head; i += nthreads) {
+      const int kk = i / d_head, d = i - kk * d_head;
+      float v = 0.f;
+      if (kk < valid) {
+        const int kj = c0 + kk;
+        const size_t tok = static_cast<size_t>(pages[kj / page_size]) * page_size + kj % page_size;
+        v = wa_to_f(cache[(tok * G + g) * d_head + d]);
+      }
+      dst[kk * ldd + d] = v;
+    }
+  }
+}
+
 constexpr int WA_WARPS = 4, WA_MAXU = 8;      // value heads up to 32 * WA_MAXU wide
 
 template <typename CT>
@@ -254,24 +296,9 @@ __global__ void __launch_bounds__(256) window_attn_tiled_kernel(WindowAttnParams
   const int nd = (dv + 3) / 4;
   for (int c0 = lo; c0 <= pos_last; c0 += WT_KEYS) {
     __syncthreads();
-    for (int i = tid; i < WT_KEYS * dk; i += 256) {
-      const int kk = i / dk, d = i - kk * dk, kj = c0 + kk;
-      float v = 0.f;
-      if (kj <= pos_last) {
-        const size_t tok = static_cast<size_t>(pages[kj / p.page_size]) * p.page_size + kj % p.page_size;
-        v = wa_to_f(kc[(tok * p.G + g) * dk + d]);
-      }
-      Ks[kk * dkp + d] = v;
-    }
-    for (int i = tid; i < WT_KEYS * dv; i += 256) {
-      const int kk = i / dv, d = i - kk * dv, kj = c0 + kk;
-      float v = 0.f;
-      if (kj <= pos_last) {
-        const size_t tok = static_cast<size_t>(pages[kj / p.page_size]) * p.page_size + kj % p.page_size;
-        v = wa_to_f(vc[(tok * p.G + g) * dv + d]);
-      }
-      Vs[kk * dvp + d] = v;
-    }
+    const int valid = min(WT_KEYS, pos_last - c0 + 1);
+    load_rows_f32<CT>(Ks, dkp, kc, pages, p.page_size, p.G, g, dk, c0, WT_KEYS, valid, tid, 256);
+    load_rows_f32<CT>(Vs, dvp, vc, pages, p.page_size, p.G, g, dv, c0, WT_KEYS, valid, tid, 256);
     __syncthreads();
     // scores of this thread's 8 keys
     float s[WT_KEYS / 4];
@@ -370,26 +397,8 @@ __global__ void __launch_bounds__(128) window_attn_group_kernel(WindowAttnParams
   for (int c0 = lo; c0 <= ps; c0 += WD_KEYS) {
     __syncthreads();
     const int nk = min(WD_KEYS, ps - c0 + 1);
-    for (int i = tid; i < WD_KEYS * dk; i += 128) {
-      const int kk = i / dk, d = i - kk * dk;
-      float v = 0.f;
-      if (kk < nk) {
-        const int kj = c0 + kk;
-        const size_t tok = static_cast<size_t>(pages[kj / p.page_size]) * p.page_size + kj % p.page_size;
-        v = wa_to_f(kc[(tok * p.G + g) * dk + d]);
-      }
-      Ks[kk * dkp + d] = v;
-    }
-    for (int i = tid; i < WD_KEYS * dv; i += 128) {
-      const int kk = i / dv, d = i - kk * dv;
-      float v = 0.f;
-      if (kk < nk) {
-        const int kj = c0 + kk;
-        const size_t tok = static_cast<size_t>(pages[kj / p.page_size]) * p.page_size + kj % p.page_size;
-        v = wa_to_f(vc[(tok * p.G + g) * dv + d]);
-      }
-      Vs[kk * dvp + d] = v;
-    }
+    load_rows_f32<CT>(Ks, dkp, kc, pages, p.page_size, p.G, g, dk, c0, WD_KEYS, nk, tid, 128);
+    load_rows_f32<CT>(Vs, dvp, vc, pages, p.page_size, p.G, g, dv, c0, WD_KEYS, nk, tid, 128);
     __syncthreads();
 #pragma unroll
     for (int u = 0; u < WD_RU; ++u) {
@@ -437,6 +446,174 @@ __global__ void __launch_bounds__(128) window_attn_group_kernel(WindowAttnParams
         float o = acc[u][v] * inv;
         if (gate) o *= 1.f / (1.f + expf(-gate[d]));
         out[d] = wa_from_f<CT>(o);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Prompt portions on the tensor cores (bf16, head sizes multiples of 16 up to 128): CTA = (tile of 64 query rows of one
+// request, query head), 4 warps x 16 rows.  Q fragments stay in registers; K / V tiles of 64 positions are staged in shared
+// memory as bf16 with 16-byte loads; S = Q K^T and O += P V run as mma.sync m16n8k16 with fp32 accumulators, the softmax
+// (scale, window mask, running max and sum) in fp32 on the accumulator fragments, P rounded to bf16 for the second product.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int FM = 64, FN = 64, F_KB = 8, F_NT = 16;      // dim <= 16 * F_KB, vdim <= 8 * F_NT
+
+__global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnParams p) {
+  extern __shared__ __align__(16) uint8_t smraw[];
+  pdl_sync();
+  const int b = p.tile_req[blockIdx.x], row0 = p.tile_row0[blockIdx.x], h = blockIdx.y;
+  const int nrows = min(row0 + FM, p.qo_indptr[b + 1]) - row0;
+  const int dk = p.dim, dv = p.vdim, ldk = dk + 8, ldv = dv + 8, nkb = dk / 16, nvp = dv / 16;
+  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smraw);      // [64][dk + 8]; holds the Q tile first
+  __nv_bfloat16* Vs = Ks + FN * ldk;                                 // [64][dv + 8]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = h / (p.H / p.G);
+  const __nv_bfloat16* q = static_cast<const __nv_bfloat16*>(p.q);
+  const int qv = dk / 8;
+  for (int i = tid; i < FM * qv; i += 128) {
+    const int r = i / qv, c = (i - r * qv) * 8;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < nrows) v = *reinterpret_cast<const uint4*>(q + (static_cast<size_t>(row0 + r) * p.H + h) * dk + c);
+    *reinterpret_cast<uint4*>(Ks + r * ldk + c) = v;
+  }
+  __syncthreads();
+  uint32_t qf[F_KB][4];
+#pragma unroll
+  for (int kb = 0; kb < F_KB; ++kb)
+    if (kb < nkb) ldmatrix_x4(qf[kb], smem_u32(Ks + (warp * 16 + (lane & 15)) * ldk + kb * 16 + (lane >> 4) * 8));
+  const int pos0 = p.pos[row0], pos_last = pos0 + nrows - 1;
+  const int rA = warp * 16 + (lane >> 2), rB = rA + 8;
+  const int posA = pos0 + rA, posB = pos0 + rB;
+  const bool okA = rA < nrows, okB = rB < nrows;
+  const int loA = p.window > 0 ? max(0, posA - p.window + 1) : 0, loB = p.window > 0 ? max(0, posB - p.window + 1) : 0;
+  const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int32_t* pages = p.page_indices + p.page_indptr[b];
+  const __nv_bfloat16* kc = static_cast<const __nv_bfloat16*>(p.k_cache);
+  const __nv_bfloat16* vc = static_cast<const __nv_bfloat16*>(p.v_cache);
+  float o[F_NT][4];
+#pragma unroll
+  for (int n = 0; n < F_NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
+  const int vv = dv / 8;
+  for (int c0 = lo; c0 <= pos_last; c0 += FN) {
+    __syncthreads();
+    for (int i = tid; i < FN * qv; i += 128) {
+      const int kk = i / qv, c = (i - kk * qv) * 8, kj = c0 + kk;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (kj <= pos_last) {
+        const size_t tok = static_cast<size_t>(pages[kj / p.page_size]) * p.page_size + kj % p.page_size;
+        v = *reinterpret_cast<const uint4*>(kc + (tok * p.G + g) * dk + c);
+      }
+      *reinterpret_cast<uint4*>(Ks + kk * ldk + c) = v;
+    }
+    for (int i = tid; i < FN * vv; i += 128) {
+      const int kk = i / vv, c = (i - kk * vv) * 8, kj = c0 + kk;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (kj <= pos_last) {
+        const size_t tok = static_cast<size_t>(pages[kj / p.page_size]) * p.page_size + kj % p.page_size;
+        v = *reinterpret_cast<const uint4*>(vc + (tok * p.G + g) * dv + c);
+      }
+      *reinterpret_cast<uint4*>(Vs + kk * ldv + c) = v;
+    }
+    __syncthreads();
+    // a warp whose 16 rows see nothing of this tile has no work in it
+    const int w_first = pos0 + warp * 16, w_last = min(pos0 + warp * 16 + 15, pos_last);
+    const int w_lo = p.window > 0 ? max(0, w_first - p.window + 1) : 0;
+    if (warp * 16 >= nrows || c0 > w_last || c0 + FN - 1 < w_lo) continue;
+    float sc[FN / 8][4];
+#pragma unroll
+    for (int n = 0; n < FN / 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+#pragma unroll
+    for (int kb = 0; kb < F_KB; ++kb) {
+      if (kb < nkb) {
+#pragma unroll
+        for (int np = 0; np < FN / 16; ++np) {
+          uint32_t kf[4];
+          ldmatrix_x4(kf, smem_u32(Ks + (np * 16 + (lane >> 4) * 8 + (lane & 7)) * ldk + kb * 16 + ((lane >> 3) & 1) * 8));
+          mma_bf16_16816(sc[2 * np], qf[kb], kf[0], kf[1]);
+          mma_bf16_16816(sc[2 * np + 1], qf[kb], kf[2], kf[3]);
+        }
+      }
+    }
+    float mxA = -INFINITY, mxB = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < FN / 8; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int kj = c0 + n * 8 + (lane & 3) * 2 + (e & 1);
+        const bool vis = e < 2 ? (okA && kj <= posA && kj >= loA) : (okB && kj <= posB && kj >= loB);
+        const float v = vis ? sc[n][e] * p.scale : -INFINITY;
+        sc[n][e] = v;
+        if (e < 2) mxA = fmaxf(mxA, v);
+        else mxB = fmaxf(mxB, v);
+      }
+    }
+    mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1));
+    mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
+    mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1));
+    mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
+    const float nA = fmaxf(mA, mxA), nB = fmaxf(mB, mxB);
+    const float cA = nA == -INFINITY ? 1.f : expf(mA - nA), cB = nB == -INFINITY ? 1.f : expf(mB - nB);
+    float sA = 0.f, sB = 0.f;
+#pragma unroll
+    for (int n = 0; n < FN / 8; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float v = sc[n][e];
+        const float pj = v == -INFINITY ? 0.f : expf(v - (e < 2 ? nA : nB));
+        sc[n][e] = pj;
+        if (e < 2) sA += pj;
+        else sB += pj;
+      }
+    }
+    sA += __shfl_xor_sync(0xffffffffu, sA, 1);
+    sA += __shfl_xor_sync(0xffffffffu, sA, 2);
+    sB += __shfl_xor_sync(0xffffffffu, sB, 1);
+    sB += __shfl_xor_sync(0xffffffffu, sB, 2);
+    lA = lA * cA + sA;
+    lB = lB * cB + sB;
+    mA = nA;
+    mB = nB;
+#pragma unroll
+    for (int n = 0; n < F_NT; ++n) {
+      o[n][0] *= cA; o[n][1] *= cA; o[n][2] *= cB; o[n][3] *= cB;
+    }
+#pragma unroll
+    for (int kb = 0; kb < FN / 16; ++kb) {
+      uint32_t pa[4];
+      pa[0] = pack_bf16(sc[2 * kb][0], sc[2 * kb][1]);
+      pa[1] = pack_bf16(sc[2 * kb][2], sc[2 * kb][3]);
+      pa[2] = pack_bf16(sc[2 * kb + 1][0], sc[2 * kb + 1][1]);
+      pa[3] = pack_bf16(sc[2 * kb + 1][2], sc[2 * kb + 1][3]);
+#pragma unroll
+      for (int np = 0; np < F_NT / 2; ++np) {
+        if (np < nvp) {
+          uint32_t vf[4];
+          ldmatrix_x4_trans(vf, smem_u32(Vs + (kb * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * ldv + np * 16 + (lane >> 4) * 8));
+          mma_bf16_16816(o[2 * np], pa, vf[0], vf[1]);
+          mma_bf16_16816(o[2 * np + 1], pa, vf[2], vf[3]);
+        }
+      }
+    }
+  }
+  const float iA = okA ? 1.f / lA : 0.f, iB = okB ? 1.f / lB : 0.f;
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
+#pragma unroll
+  for (int n = 0; n < F_NT; ++n) {
+    const int d = n * 8 + (lane & 3) * 2;
+    if (d < dv) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        if (!(half ? okB : okA)) continue;
+        const int t = row0 + (half ? rB : rA);
+        float x0 = o[n][2 * half] * (half ? iB : iA), x1 = o[n][2 * half + 1] * (half ? iB : iA);
+        if (p.gate) {
+          const float* gt = p.gate + static_cast<size_t>(t) * p.ld_gate + h * dv + d;
+          x0 *= 1.f / (1.f + expf(-gt[0]));
+          x1 *= 1.f / (1.f + expf(-gt[1]));
+        }
+        *reinterpret_cast<uint32_t*>(out + static_cast<size_t>(t) * p.H * dv + h * dv + d) = pack_bf16(x0, x1);
       }
     }
   }
@@ -523,10 +700,15 @@ int vb_window_attn_tiled(void* d_out, const void* d_q, const void* d_k_cache, co
   if (n_tiles <= 0) return 0;
   WindowAttnParams p{d_q, d_k_cache, d_v_cache, d_out, d_gate, ld_gate, nullptr, d_pos, d_page_indptr, d_page_indices,
                      d_qo_indptr, d_tile_req, d_tile_row0, T, H, G, dim, vdim, page_size, window, scale};
+  dim3 grid(n_tiles, H);
+  if (dtype == 0 && dim % 16 == 0 && vdim % 16 == 0 && dim <= 16 * F_KB && vdim <= 8 * F_NT) {
+    const size_t msmem = static_cast<size_t>(FN) * (dim + 8 + vdim + 8) * sizeof(__nv_bfloat16);
+    VB_LAUNCH_PDL(window_attn_mma_kernel, grid, 128, msmem, stream, p);
+    return 0;
+  }
   const size_t smem = (static_cast<size_t>(WT_ROWS + WT_KEYS) * (dim + 1) + static_cast<size_t>(WT_KEYS) * (vdim + 1) +
                        static_cast<size_t>(WT_ROWS) * (WT_KEYS + 1)) * sizeof(float);
   VB_CHECK_ARG(smem <= static_cast<size_t>(VB_MAX_DYN_SMEM), "vb_window_attn_tiled: heads too large for shared memory");
-  dim3 grid(n_tiles, H);
   if (dtype == 1) {
     VB_CHECK_CUDA(cudaFuncSetAttribute(window_attn_tiled_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
     VB_LAUNCH_PDL(window_attn_tiled_kernel<float>, grid, 256, smem, stream, p);

@@ -356,6 +356,8 @@ class HybridEngine:
             self.moe_out = torch.zeros(R * top * W, dtype=F32, device=dev)
             self.s_act = torch.zeros(R * max([f.shared_ff for f in moe] + [1]), dtype=CT, device=dev)
             self.s_out = torch.zeros(R, W, dtype=F32, device=dev)
+        self.sms = ops.device_info()[0] if dev.type == "cuda" else 1
+        self.partials = torch.zeros(2 * self.sms * 128 * 256 if weights.tensor_core else 4, dtype=F32, device=dev)
         self.hn = torch.zeros(max_out_rows, W, dtype=CT, device=dev)
         self.logits = torch.zeros(max_out_rows, cfg.vocab, dtype=F32, device=dev)
         self.first_vmix = next((i for i, L in enumerate(cfg.layers) if L.kind == "attention" and L.mixer.v_mix), None)
@@ -367,7 +369,14 @@ class HybridEngine:
         """out (fp32) = alpha * x @ w^T: the tcgen05 kernel for packed bf16 weights, the fp32-FMA kernel otherwise."""
         if isinstance(w, ops.PackedWeight):
             assert alpha == 1.0 and out.dtype == F32 and out.is_contiguous()
-            ops.gemm(x, w, mode=1, split_k=1, out=out.view(1, x.shape[0], w.N))
+            T = x.shape[0]
+            # skinny problems (few weight tiles x token tiles) are split along k over all SMs into fp32 planes
+            split = ops.choose_split_k(w.N, w.K, T, self.sms) if (T * w.N) % 4 == 0 else 1
+            if split > 1 and split * T * w.N <= self.partials.numel():
+                planes = self.partials[:split * T * w.N].view(split, T, w.N)
+                ops.gemm(x, w, mode=1, split_k=split, out=planes)
+                return ops.sum_planes_f32(planes, out)
+            ops.gemm(x, w, mode=1, split_k=1, out=out.view(1, T, w.N))
             return out
         return ops.linear(x, w, out, alpha=alpha)
 

@@ -978,6 +978,14 @@ def cast_f32_bf16(src: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def sum_planes_f32(partials: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out = partials.sum(0) in plane order; partials fp32 [planes, ...] contiguous."""
+    _need_cuda(partials, out)
+    assert partials.dtype == F32 and out.dtype == F32 and partials.is_contiguous() and out.is_contiguous()
+    call("vb_sum_planes_f32", out.data_ptr(), partials.data_ptr(), partials.shape[0], out.numel(), _stream())
+    return out
+
+
 def rotary_table(pos: torch.Tensor, freq: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out [T, 2, half] fp32 = cos | sin of pos[t] * freq[j]; freq float64 [half]."""
     _need_cuda(pos, freq, out)
