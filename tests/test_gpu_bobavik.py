@@ -269,7 +269,10 @@ def _attention_case(window, n_tokens, page_size, hot, dtype, tiled, H=2, G=1, dk
         R = ops.window_attn_tile_rows()
         r0 = torch.arange(0, T, R, dtype=I32, device=DEV)
         tiles = (torch.tensor([0, T], dtype=I32, device=DEV), torch.zeros_like(r0), r0, r0.numel())
-    ops.window_attn(qo, kc, vc, out, None, row_req, pos, indptr, perm.to(DEV), T, H, G, dk, dv, window, 1.0, tiles=tiles)
+    # (the scratch lets the per-row kernel deal a row's key tiles to several CTAs when the rows are few)
+    scratch = torch.full((T * H * 8 * (dv + 2),), float("nan"), dtype=F32, device=DEV)
+    ops.window_attn(qo, kc, vc, out, None, row_req, pos, indptr, perm.to(DEV), T, H, G, dk, dv, window, 1.0, tiles=tiles,
+                    scratch=scratch)
     ref = O.window_attention(q.double(), k.double(), v.double(), 1.0, window)
     return out.float().cpu().view(T, H, dv), ref
 

@@ -114,7 +114,7 @@ SIGNATURES = {
     "vb_qkv_rotary_append": (c_int, [P, c_int, c_int, c_int, c_int, P, c_int, P, P, P, P, P, P, P, c_int, c_int, c_int,
                                      c_int, c_int, c_int, c_int, P, P, c_int, P]),
     "vb_window_attn": (c_int, [P, P, P, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                               c_int, P]),
+                               c_int, P, C.c_longlong, P]),
     "vb_window_attn_tile_rows": (c_int, []),
     "vb_window_attn_tiled": (c_int, [P, P, P, P, P, c_int, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
                                      c_int, c_int, c_float, c_int, P]),
@@ -189,7 +189,7 @@ def check(rc: int, what: str = ""):
 # kernels (+ memset nodes) each entry point enqueues; everything not listed launches exactly one
 LAUNCHES = {"vb_set_pdl": 0, "vb_set_trace": 0, "vb_weight_tiles_bytes": 0, "vb_tensor_map_kv": 0,
             "vb_tensor_map_2d_bf16": 0, "vb_device_info": 0, "vb_sample": 1, "vb_update_repetition_cache": 1,
-            "vb_set_gemm_smem_kb": 0, "vb_window_attn_tile_rows": 0, "vb_decay_attn_tile_rows": 0, "vb_decay_attn_tiled": 3}
+            "vb_set_gemm_smem_kb": 0, "vb_window_attn_tile_rows": 0, "vb_decay_attn_tile_rows": 0, "vb_decay_attn_tiled": 3, "vb_window_attn": 2}
 launch_counter = [0]
 
 

@@ -226,11 +226,19 @@ __global__ void __launch_bounds__(256) decay_tile_scan_kernel(DecayTileParams tp
   float* S = p.state + (static_cast<size_t>(p.slots[b]) * p.H + h) * per;
   for (size_t i = blockIdx.z * blockDim.x + threadIdx.x; i < per; i += static_cast<size_t>(gridDim.z) * blockDim.x) {
     float s = fresh ? 0.f : S[i];
-    for (int c = 0; c < n_tiles; ++c) {
-      float* u = tp.scratch + (static_cast<size_t>(first + c) * p.H + h) * per + i;
-      const float uv = *u;
-      *u = s;
-      s = (c == n_tiles - 1 ? d_last : d_full) * s + uv;
+    for (int c0 = 0; c0 < n_tiles; c0 += 8) {          // eight independent loads in flight, then the serial update
+      float uv[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        uv[j] = c0 + j < n_tiles ? tp.scratch[(static_cast<size_t>(first + c0 + j) * p.H + h) * per + i] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int c = c0 + j;
+        if (c < n_tiles) {
+          tp.scratch[(static_cast<size_t>(first + c) * p.H + h) * per + i] = s;
+          s = (c == n_tiles - 1 ? d_last : d_full) * s + uv[j];
+        }
+      }
     }
     S[i] = s;
   }

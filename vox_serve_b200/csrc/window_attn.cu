@@ -115,6 +115,8 @@ struct WindowAttnParams {
   const int32_t* tile_row0;   // tiled kernel: first row of tile i
   int T, H, G, dim, vdim, page_size, window;   // window <= 0: every earlier position is visible
   float scale;
+  int splits;                 // grouped kernel: key tiles are dealt round-robin to `splits` CTAs per (row, key/value head)
+  float* part;                // [T][H][splits][vdim + 2]: unnormalised output, running max, running sum of every split
 };
 
 template <typename CT>
@@ -394,7 +396,8 @@ __global__ void __launch_bounds__(128) window_attn_group_kernel(WindowAttnParams
 #pragma unroll
     for (int v = 0; v < WD_VU; ++v) acc[u][v] = 0.f;
   }
-  for (int c0 = lo; c0 <= ps; c0 += WD_KEYS) {
+  const int S = p.splits, sidx = blockIdx.z;
+  for (int c0 = lo + sidx * WD_KEYS; c0 <= ps; c0 += S * WD_KEYS) {
     __syncthreads();
     const int nk = min(WD_KEYS, ps - c0 + 1);
     load_rows_f32<CT>(Ks, dkp, kc, pages, p.page_size, p.G, g, dk, c0, WD_KEYS, nk, tid, 128);
@@ -436,6 +439,19 @@ __global__ void __launch_bounds__(128) window_attn_group_kernel(WindowAttnParams
     const int r = warp + 4 * u;
     if (r >= R) break;
     const int h = g * R + r;
+    if (S > 1) {              // leave this split's share for vb::window_attn_merge_kernel
+      float* pt = p.part + ((static_cast<size_t>(t) * p.H + h) * S + sidx) * (dv + 2);
+#pragma unroll
+      for (int v = 0; v < WD_VU; ++v) {
+        const int d = lane + 32 * v;
+        if (d < dv) pt[d] = acc[u][v];
+      }
+      if (lane == 0) {
+        pt[dv] = m[u];
+        pt[dv + 1] = l[u];
+      }
+      continue;
+    }
     const float inv = 1.f / l[u];
     CT* out = static_cast<CT*>(p.out) + static_cast<size_t>(t) * p.H * dv + h * dv;
     const float* gate = p.gate ? p.gate + static_cast<size_t>(t) * p.ld_gate + h * dv : nullptr;
@@ -448,6 +464,28 @@ __global__ void __launch_bounds__(128) window_attn_group_kernel(WindowAttnParams
         out[d] = wa_from_f<CT>(o);
       }
     }
+  }
+}
+
+// merges the splits of a (row, head): out = sum_s acc_s e^(m_s - M) / sum_s l_s e^(m_s - M), then the gate
+template <typename CT>
+__global__ void __launch_bounds__(64) window_attn_merge_kernel(WindowAttnParams p) {
+  pdl_sync();
+  const int t = blockIdx.x, h = blockIdx.y, S = p.splits, dv = p.vdim;
+  const float* pt = p.part + (static_cast<size_t>(t) * p.H + h) * S * (dv + 2);
+  float M = -INFINITY;
+  for (int s = 0; s < S; ++s) M = fmaxf(M, pt[s * (dv + 2) + dv]);
+  float L = 0.f;
+  for (int s = 0; s < S; ++s) L += pt[s * (dv + 2) + dv + 1] * expf(pt[s * (dv + 2) + dv] - M);
+  const float inv = 1.f / L;
+  CT* out = static_cast<CT*>(p.out) + static_cast<size_t>(t) * p.H * dv + h * dv;
+  const float* gate = p.gate ? p.gate + static_cast<size_t>(t) * p.ld_gate + h * dv : nullptr;
+  for (int d = threadIdx.x; d < dv; d += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < S; ++s) a += pt[s * (dv + 2) + d] * expf(pt[s * (dv + 2) + dv] - M);
+    float o = a * inv;
+    if (gate) o *= 1.f / (1.f + expf(-gate[d]));
+    out[d] = wa_from_f<CT>(o);
   }
 }
 
@@ -654,27 +692,37 @@ int vb_qkv_rotary_append(const float* d_proj, int ldp, int q_off, int k_off, int
 int vb_window_attn(void* d_out, const void* d_q, const void* d_k_cache, const void* d_v_cache, const float* d_gate,
                    int ld_gate, const int32_t* d_row_req, const int32_t* d_pos, const int32_t* d_page_indptr,
                    const int32_t* d_page_indices, int T, int H, int G, int dim, int vdim, int page_size, int window,
-                   float scale, int dtype, void* stream) {
+                   float scale, int dtype, float* d_part, long long part_floats, void* stream) {
   VB_CHECK_ARG(d_out && d_q && d_k_cache && d_v_cache && d_row_req && d_pos && d_page_indptr && d_page_indices,
                "vb_window_attn: null pointer");
   VB_CHECK_ARG(H > 0 && G > 0 && H % G == 0 && dim > 0 && vdim > 0 && vdim <= 32 * WA_MAXU && page_size > 0,
                "vb_window_attn: bad sizes H=%d G=%d dim=%d vdim=%d (vdim <= %d)", H, G, dim, vdim, 32 * WA_MAXU);
   if (T <= 0) return 0;
   WindowAttnParams p{d_q, d_k_cache, d_v_cache, d_out, d_gate, ld_gate, d_row_req, d_pos, d_page_indptr, d_page_indices,
-                     nullptr, nullptr, nullptr, T, H, G, dim, vdim, page_size, window, scale};
+                     nullptr, nullptr, nullptr, T, H, G, dim, vdim, page_size, window, scale, 1, d_part};
   // a CTA per (row, key/value head) with the K / V tiles shared by the group's query heads, when the group fits its
   // registers and the tiles fit shared memory; one warp per (row, query head) otherwise
   const int R = H / G;
   const size_t gsmem = (static_cast<size_t>(R) * dim + static_cast<size_t>(WD_KEYS) * (dim + 1 + vdim + 1) +
                         static_cast<size_t>(R) * WD_KEYS) * sizeof(float);
   if (R <= 4 * WD_RU && vdim <= 32 * WD_VU && gsmem <= 96 * 1024) {
-    dim3 ggrid(T, G);
+    // few rows leave most SMs idle and every CTA a long serial walk: deal the key tiles of a row to several CTAs
+    // (about four CTAs per SM in all) and merge their shares; needs the scratch buffer
+    int splits = 1;
+    if (d_part) {
+      splits = max(1, min(8, (4 * 148) / max(1, T * G)));
+      while (splits > 1 && static_cast<long long>(T) * H * splits * (vdim + 2) > part_floats) --splits;
+    }
+    p.splits = splits;
+    dim3 ggrid(T, G, splits);
     if (dtype == 1) {
       VB_CHECK_CUDA(cudaFuncSetAttribute(window_attn_group_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
       VB_LAUNCH_PDL(window_attn_group_kernel<float>, ggrid, 128, gsmem, stream, p);
+      if (splits > 1) VB_LAUNCH_PDL(window_attn_merge_kernel<float>, dim3(T, H), 64, 0, stream, p);
     } else {
       VB_CHECK_CUDA(cudaFuncSetAttribute(window_attn_group_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
       VB_LAUNCH_PDL(window_attn_group_kernel<bf16>, ggrid, 128, gsmem, stream, p);
+      if (splits > 1) VB_LAUNCH_PDL(window_attn_merge_kernel<bf16>, dim3(T, H), 64, 0, stream, p);
     }
     return 0;
   }
@@ -699,7 +747,7 @@ int vb_window_attn_tiled(void* d_out, const void* d_q, const void* d_k_cache, co
                "vb_window_attn_tiled: bad sizes H=%d G=%d dim=%d vdim=%d", H, G, dim, vdim);
   if (n_tiles <= 0) return 0;
   WindowAttnParams p{d_q, d_k_cache, d_v_cache, d_out, d_gate, ld_gate, nullptr, d_pos, d_page_indptr, d_page_indices,
-                     d_qo_indptr, d_tile_req, d_tile_row0, T, H, G, dim, vdim, page_size, window, scale};
+                     d_qo_indptr, d_tile_req, d_tile_row0, T, H, G, dim, vdim, page_size, window, scale, 1, nullptr};
   dim3 grid(n_tiles, H);
   if (dtype == 0 && dim % 16 == 0 && vdim % 16 == 0 && dim <= 16 * F_KB && vdim <= 8 * F_NT) {
     const size_t msmem = static_cast<size_t>(FN) * (dim + 8 + vdim + 8) * sizeof(__nv_bfloat16);

@@ -336,6 +336,8 @@ class HybridEngine:
             n_t = max_rows // self.lin_tile_rows + max_out_rows + 1
             self.lin_scratch = torch.zeros(n_t * max(m.heads * m.dim * m.vdim for m in tiled), dtype=F32, device=dev)
         self.v_first = torch.zeros(R * max([m.kv_heads * m.vdim for m in att if m.v_mix] + [1]), dtype=F32, device=dev)
+        # split-key scratch of the per-row attention kernel: steps of up to 256 rows, 8 splits
+        self.attn_part = torch.zeros(256 * 8 * max([m.heads * (m.vdim + 2) for m in att] + [1]), dtype=F32, device=dev)
         self.freqs: Dict[Tuple, torch.Tensor] = {}
         self.cs: Dict[Tuple, torch.Tensor] = {}
         for m in att:
@@ -405,7 +407,7 @@ class HybridEngine:
         else:
             # decode rows (and mixed steps: single rows and portions together) on the warp-per-row kernel
             ops.window_attn(q, self.cache.k[i], self.cache.v[i], out, gate, s.row_req, s.pos, s.page_indptr, s.page_indices,
-                            T, m.heads, m.kv_heads, m.dim, m.vdim, m.window, m.scale)
+                            T, m.heads, m.kv_heads, m.dim, m.vdim, m.window, m.scale, scratch=self.attn_part)
         self._proj(out, w["o"], self.y[:T])
 
     def _lightning(self, i: int, m: DecayAttentionConfig, w: Dict[str, Any], s: StepInputs) -> None:
