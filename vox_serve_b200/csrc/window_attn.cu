@@ -503,8 +503,8 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnParams p
   const int b = p.tile_req[blockIdx.x], row0 = p.tile_row0[blockIdx.x], h = blockIdx.y;
   const int nrows = min(row0 + FM, p.qo_indptr[b + 1]) - row0;
   const int dk = p.dim, dv = p.vdim, ldk = dk + 8, ldv = dv + 8, nkb = dk / 16, nvp = dv / 16;
-  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smraw);      // [64][dk + 8]; holds the Q tile first
-  __nv_bfloat16* Vs = Ks + FN * ldk;                                 // [64][dv + 8]
+  // two stages of K [64][dk + 8] | V [64][dv + 8]; the first stage's K region holds the Q tile first
+  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smraw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = h / (p.H / p.G);
   const __nv_bfloat16* q = static_cast<const __nv_bfloat16*>(p.q);
@@ -534,31 +534,43 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnParams p
   for (int n = 0; n < F_NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
   float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
   const int vv = dv / 8;
-  for (int c0 = lo; c0 <= pos_last; c0 += FN) {
-    __syncthreads();
-    for (int i = tid; i < FN * qv; i += 128) {
-      const int kk = i / qv, c = (i - kk * qv) * 8, kj = c0 + kk;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (kj <= pos_last) {
-        const size_t tok = static_cast<size_t>(pages[kj / p.page_size]) * p.page_size + kj % p.page_size;
-        v = *reinterpret_cast<const uint4*>(kc + (tok * p.G + g) * dk + c);
-      }
-      *reinterpret_cast<uint4*>(Ks + kk * ldk + c) = v;
+  // K / V tiles are double-buffered: the asynchronous copies of tile i + 1 are in flight while tile i is multiplied
+  // (cp.async of 16 bytes; rows past the request's last position are filled with zeros by a zero source size)
+  const int stage_elems = FN * (ldk + ldv);
+  auto issue_tile = [&](int c0, int stage) {
+    __nv_bfloat16* Kd = Ks + stage * stage_elems;
+    __nv_bfloat16* Vd = Kd + FN * ldk;
+    for (int i = tid; i < FN * (qv + vv); i += 128) {
+      const bool is_k = i < FN * qv;
+      const int j = is_k ? i : i - FN * qv, per = is_k ? qv : vv;
+      const int kk = j / per, c = (j - kk * per) * 8, kj = c0 + kk;
+      const bool ok = kj <= pos_last;
+      const int kq = ok ? kj : pos_last;                 // (a valid address also for the zero-filled rows)
+      const size_t tok = static_cast<size_t>(pages[kq / p.page_size]) * p.page_size + kq % p.page_size;
+      const __nv_bfloat16* src = is_k ? kc + (tok * p.G + g) * dk + c : vc + (tok * p.G + g) * dv + c;
+      const uint32_t dst = smem_u32(is_k ? Kd + kk * ldk + c : Vd + kk * ldv + c);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(ok ? 16 : 0) : "memory");
     }
-    for (int i = tid; i < FN * vv; i += 128) {
-      const int kk = i / vv, c = (i - kk * vv) * 8, kj = c0 + kk;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (kj <= pos_last) {
-        const size_t tok = static_cast<size_t>(pages[kj / p.page_size]) * p.page_size + kj % p.page_size;
-        v = *reinterpret_cast<const uint4*>(vc + (tok * p.G + g) * dv + c);
-      }
-      *reinterpret_cast<uint4*>(Vs + kk * ldv + c) = v;
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  __syncthreads();                    // every warp holds its Q fragments: the first stage may be overwritten
+  issue_tile(lo, 0);
+  int stage = 0;
+  for (int c0 = lo; c0 <= pos_last; c0 += FN, stage ^= 1) {
+    if (c0 + FN <= pos_last) {
+      issue_tile(c0 + FN, stage ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
+    const __nv_bfloat16* Kt = Ks + stage * stage_elems;
+    const __nv_bfloat16* Vt = Kt + FN * ldk;
     // a warp whose 16 rows see nothing of this tile has no work in it
     const int w_first = pos0 + warp * 16, w_last = min(pos0 + warp * 16 + 15, pos_last);
     const int w_lo = p.window > 0 ? max(0, w_first - p.window + 1) : 0;
-    if (warp * 16 >= nrows || c0 > w_last || c0 + FN - 1 < w_lo) continue;
+    const bool idle = warp * 16 >= nrows || c0 > w_last || c0 + FN - 1 < w_lo;
+    if (!idle) {
     float sc[FN / 8][4];
 #pragma unroll
     for (int n = 0; n < FN / 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
@@ -568,7 +580,7 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnParams p
 #pragma unroll
         for (int np = 0; np < FN / 16; ++np) {
           uint32_t kf[4];
-          ldmatrix_x4(kf, smem_u32(Ks + (np * 16 + (lane >> 4) * 8 + (lane & 7)) * ldk + kb * 16 + ((lane >> 3) & 1) * 8));
+          ldmatrix_x4(kf, smem_u32(Kt + (np * 16 + (lane >> 4) * 8 + (lane & 7)) * ldk + kb * 16 + ((lane >> 3) & 1) * 8));
           mma_bf16_16816(sc[2 * np], qf[kb], kf[0], kf[1]);
           mma_bf16_16816(sc[2 * np + 1], qf[kb], kf[2], kf[3]);
         }
@@ -628,12 +640,14 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnParams p
       for (int np = 0; np < F_NT / 2; ++np) {
         if (np < nvp) {
           uint32_t vf[4];
-          ldmatrix_x4_trans(vf, smem_u32(Vs + (kb * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * ldv + np * 16 + (lane >> 4) * 8));
+          ldmatrix_x4_trans(vf, smem_u32(Vt + (kb * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * ldv + np * 16 + (lane >> 4) * 8));
           mma_bf16_16816(o[2 * np], pa, vf[0], vf[1]);
           mma_bf16_16816(o[2 * np + 1], pa, vf[2], vf[3]);
         }
       }
     }
+    }
+    __syncthreads();                  // this stage is free for the copies of the tile after the next
   }
   const float iA = okA ? 1.f / lA : 0.f, iB = okB ? 1.f / lB : 0.f;
   __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
@@ -750,7 +764,8 @@ int vb_window_attn_tiled(void* d_out, const void* d_q, const void* d_k_cache, co
                      d_qo_indptr, d_tile_req, d_tile_row0, T, H, G, dim, vdim, page_size, window, scale, 1, nullptr};
   dim3 grid(n_tiles, H);
   if (dtype == 0 && dim % 16 == 0 && vdim % 16 == 0 && dim <= 16 * F_KB && vdim <= 8 * F_NT) {
-    const size_t msmem = static_cast<size_t>(FN) * (dim + 8 + vdim + 8) * sizeof(__nv_bfloat16);
+    const size_t msmem = 2 * static_cast<size_t>(FN) * (dim + 8 + vdim + 8) * sizeof(__nv_bfloat16);      // two stages
+    VB_CHECK_CUDA(cudaFuncSetAttribute(window_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
     VB_LAUNCH_PDL(window_attn_mma_kernel, grid, 128, msmem, stream, p);
     return 0;
   }
