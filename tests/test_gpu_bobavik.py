@@ -177,6 +177,21 @@ def test_each_mixer_alone(layers):
 
 
 @pytest.mark.gpu
+def test_bfloat16_without_tensor_core_shapes():
+    """a width that is no multiple of 8 and an expert axis that is none either: every bfloat16 projection runs on the
+    fp32-FMA kernel and the experts in their grouped form."""
+    cfg = O.make_config(width=68, layers=("attention", "lightning"), ff=18, shared_ff=36, experts=4, top=2, vdim=8)
+    sd = O.random_weights(cfg, 17)
+    toks = _tokens(60, cfg["vocab"], 3)
+    ref = O.forward(cfg, sd, toks)
+    w = _worker(cfg, sd, BF16)
+    assert isinstance(w.engine.w.layers[0]["qkvg"], torch.Tensor)           # not re-tiled for the tcgen05 kernel
+    assert "gu" in w.engine.w.layers[0] and "gu_all" not in w.engine.w.layers[0]
+    got = _replay(w, {"a": toks}, [[("a", 21)], [("a", 2)], [("a", 30)]] + [[("a", 1)]] * 7)["a"]
+    assert _err(got, ref) < TOL[BF16]
+
+
+@pytest.mark.gpu
 def test_other_sizes():
     """sizes and constants that differ between layers and from the defaults: kv_heads = heads and = 1, vdim = dim and
     > dim, rotary on the whole head / a slice / absent, no frequency scaling, window 1 and none, top = 1 and = experts, no
