@@ -198,11 +198,43 @@ __global__ void __launch_bounds__(256) decay_tile_state_kernel(DecayTileParams t
   }
   __syncthreads();
   float* U = tp.scratch + ((static_cast<size_t>(tile) * p.H + h) * dk) * p.vdim;
-  for (int i = tid; i < dk * DV; i += 256) {
-    const int k = i / DV, e = i - k * DV;
-    float a = 0.f;
-    for (int j = 0; j < L; ++j) a = fmaf(pw[L - 1 - j] * Sk[j * dkp + k], Sv[j * dvp + e], a);
-    U[static_cast<size_t>(k) * p.vdim + e0 + e] = a;
+  // register tiles: thread (ty, tx) owns key dims ty + 16 i and value dims tx + 16 e; per position it reads its key values
+  // (two distinct rows of addresses per warp: broadcast) and value values (consecutive addresses) once for 32 FMAs
+  const int tx = tid & 15, ty = tid >> 4;
+  for (int kb = 0; kb < dk; kb += 128) {
+    float acc[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[i][e] = 0.f;
+    for (int j = 0; j < L; ++j) {
+      const float w = pw[L - 1 - j];
+      float kv[8], vv[4];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int k = kb + ty + 16 * i;
+        kv[i] = k < dk ? Sk[j * dkp + k] : 0.f;
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int ee = tx + 16 * e;
+        vv[e] = ee < DV ? w * Sv[j * dvp + ee] : 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[i][e] = fmaf(kv[i], vv[e], acc[i][e]);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int k = kb + ty + 16 * i;
+      if (k >= dk) continue;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int ee = tx + 16 * e;
+        if (ee < DV) U[static_cast<size_t>(k) * p.vdim + e0 + ee] = acc[i][e];
+      }
+    }
   }
 }
 
@@ -283,26 +315,80 @@ __global__ void __launch_bounds__(256) decay_tile_out_kernel(DecayTileParams tp)
     Sv[r * dvp + e] = r < L ? silu_f(p.proj[static_cast<size_t>(row0 + r) * p.ldp + p.v_off + h * p.vdim + e0 + e]) : 0.f;
   }
   __syncthreads();
-  for (int i = tid; i < C * C; i += 256) {
-    const int r = i / C, j = i - r * C;
-    float a = 0.f;
-    if (j <= r && r < L) {
-      const float* qr = Sq + r * dkp;
-      const float* kr = Sk + j * dkp;
-      for (int k = 0; k < dk; ++k) a = fmaf(qr[k], kr[k], a);
-      a *= pw[r - j];
+  // register tiles (C = 64, 16 x 16 threads): thread (ty, tx) owns rows ty + 16 i and columns tx + 16 j
+  const int tx = tid & 15, ty = tid >> 4;
+  {
+    float a[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) a[i][j] = 0.f;
+    for (int k = 0; k < dk; ++k) {
+      float qv[4], kv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) qv[i] = Sq[(ty + 16 * i) * dkp + k];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) kv[j] = Sk[(tx + 16 * j) * dkp + k];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) a[i][j] = fmaf(qv[i], kv[j], a[i][j]);
     }
-    Sa[r * (C + 1) + j] = a;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int r = ty + 16 * i, c = tx + 16 * j;
+        Sa[r * (C + 1) + c] = (c <= r && r < L) ? a[i][j] * pw[r - c] : 0.f;
+      }
   }
   __syncthreads();
-  for (int i = tid; i < L * DV; i += 256) {
-    const int r = i / DV, e = i - r * DV;
-    float intra = 0.f, inter = 0.f;
-    const float* ar = Sa + r * (C + 1);
-    for (int j = 0; j <= r; ++j) intra = fmaf(ar[j], Sv[j * dvp + e], intra);
-    const float* qr = Sq + r * dkp;
-    for (int k = 0; k < dk; ++k) inter = fmaf(qr[k], Ss[k * dvp + e], inter);
-    p.out[static_cast<size_t>(row0 + r) * p.H * p.vdim + h * p.vdim + e0 + e] = intra + pw[r + 1] * inter;
+  {
+    float intra[4][4], inter[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) intra[i][e] = inter[i][e] = 0.f;
+    const int jmax = min(L, ty + 49);              // the thread's last row is ty + 48: later positions are masked for all
+    for (int j = 0; j < jmax; ++j) {
+      float av[4], vv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) av[i] = Sa[(ty + 16 * i) * (C + 1) + j];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int ee = tx + 16 * e;
+        vv[e] = ee < DV ? Sv[j * dvp + ee] : 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) intra[i][e] = fmaf(av[i], vv[e], intra[i][e]);
+    }
+    for (int k = 0; k < dk; ++k) {
+      float qv[4], sv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) qv[i] = Sq[(ty + 16 * i) * dkp + k];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int ee = tx + 16 * e;
+        sv[e] = ee < DV ? Ss[k * dvp + ee] : 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) inter[i][e] = fmaf(qv[i], sv[e], inter[i][e]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = ty + 16 * i;
+      if (r >= L) continue;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int ee = tx + 16 * e;
+        if (ee < DV)
+          p.out[static_cast<size_t>(row0 + r) * p.H * p.vdim + h * p.vdim + e0 + ee] = intra[i][e] + pw[r + 1] * inter[i][e];
+      }
+    }
   }
 }
 

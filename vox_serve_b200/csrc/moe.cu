@@ -19,22 +19,30 @@
 namespace vb {
 
 template <typename XT>
-__global__ void __launch_bounds__(128) moe_route_kernel(int32_t* __restrict__ idx, float* __restrict__ wts,
+__global__ void __launch_bounds__(256) moe_route_kernel(int32_t* __restrict__ idx, float* __restrict__ wts,
                                                         const XT* __restrict__ h, const float* __restrict__ wr,
                                                         const float* __restrict__ br, int W, int E, int top) {
-  extern __shared__ float z[];      // [E]
+  extern __shared__ float z[];      // [E] logits, then the row as fp32 [W]
+  float* xs = z + E;
   pdl_sync();
   const size_t t = blockIdx.x;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const XT* x = h + t * W;
-  for (int e = warp; e < E; e += 4) {
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    if constexpr (sizeof(XT) == 4) xs[i] = x[i];
+    else xs[i] = __bfloat162float(x[i]);
+  }
+  __syncthreads();
+  for (int e = warp; e < E; e += nw) {
     const float* w = wr + static_cast<size_t>(e) * W;
     float s = 0.f;
-    for (int i = lane; i < W; i += 32) {
-      float xv;
-      if constexpr (sizeof(XT) == 4) xv = x[i];
-      else xv = __bfloat162float(x[i]);
-      s = fmaf(xv, w[i], s);
+    if ((W & 3) == 0) {
+      for (int i = lane * 4; i < W; i += 128) {
+        const float4 wv = *reinterpret_cast<const float4*>(w + i);
+        s = fmaf(xs[i], wv.x, s); s = fmaf(xs[i + 1], wv.y, s); s = fmaf(xs[i + 2], wv.z, s); s = fmaf(xs[i + 3], wv.w, s);
+      }
+    } else {
+      for (int i = lane; i < W; i += 32) s = fmaf(xs[i], w[i], s);
     }
     s = warp_sum(s);
     if (lane == 0) z[e] = s + (br ? br[e] : 0.f);
@@ -145,9 +153,10 @@ int vb_moe_route(int32_t* d_idx, float* d_wts, const void* d_h, const float* d_r
   VB_CHECK_ARG(experts >= 1 && experts <= 1024 && top >= 1 && top <= 32 && top <= experts,
                "vb_moe_route: experts %d (<= 1024), top %d (<= 32, <= experts)", experts, top);
   if (T <= 0) return 0;
-  const size_t smem = static_cast<size_t>(experts) * sizeof(float);
-  if (h_dtype == 1) VB_LAUNCH_PDL(moe_route_kernel<float>, T, 128, smem, stream, d_idx, d_wts, static_cast<const float*>(d_h), d_router_w, d_router_b, width, experts, top);
-  else VB_LAUNCH_PDL(moe_route_kernel<__nv_bfloat16>, T, 128, smem, stream, d_idx, d_wts, static_cast<const __nv_bfloat16*>(d_h), d_router_w, d_router_b, width, experts, top);
+  const size_t smem = (static_cast<size_t>(experts) + width) * sizeof(float);
+  VB_CHECK_ARG(smem <= 48 * 1024, "vb_moe_route: width %d too large", width);
+  if (h_dtype == 1) VB_LAUNCH_PDL(moe_route_kernel<float>, T, 256, smem, stream, d_idx, d_wts, static_cast<const float*>(d_h), d_router_w, d_router_b, width, experts, top);
+  else VB_LAUNCH_PDL(moe_route_kernel<__nv_bfloat16>, T, 256, smem, stream, d_idx, d_wts, static_cast<const __nv_bfloat16*>(d_h), d_router_w, d_router_b, width, experts, top);
   return 0;
 }
 

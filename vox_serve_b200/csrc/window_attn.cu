@@ -537,19 +537,26 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnParams p
   // K / V tiles are double-buffered: the asynchronous copies of tile i + 1 are in flight while tile i is multiplied
   // (cp.async of 16 bytes; rows past the request's last position are filled with zeros by a zero source size)
   const int stage_elems = FN * (ldk + ldv);
+  // thread t copies 16-byte piece (t % 16) + 16 n of rows (t / 16) + 8 m: the page lookup and the row's cache offset are
+  // computed once per row and serve its K and its V pieces
   auto issue_tile = [&](int c0, int stage) {
     __nv_bfloat16* Kd = Ks + stage * stage_elems;
     __nv_bfloat16* Vd = Kd + FN * ldk;
-    for (int i = tid; i < FN * (qv + vv); i += 128) {
-      const bool is_k = i < FN * qv;
-      const int j = is_k ? i : i - FN * qv, per = is_k ? qv : vv;
-      const int kk = j / per, c = (j - kk * per) * 8, kj = c0 + kk;
+    const int piece = tid & 15;
+#pragma unroll 2
+    for (int kk = tid >> 4; kk < FN; kk += 8) {
+      const int kj = c0 + kk;
       const bool ok = kj <= pos_last;
       const int kq = ok ? kj : pos_last;                 // (a valid address also for the zero-filled rows)
-      const size_t tok = static_cast<size_t>(pages[kq / p.page_size]) * p.page_size + kq % p.page_size;
-      const __nv_bfloat16* src = is_k ? kc + (tok * p.G + g) * dk + c : vc + (tok * p.G + g) * dv + c;
-      const uint32_t dst = smem_u32(is_k ? Kd + kk * ldk + c : Vd + kk * ldv + c);
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(ok ? 16 : 0) : "memory");
+      const int pg = kq / p.page_size;
+      const size_t tok = (static_cast<size_t>(pages[pg]) * p.page_size + (kq - pg * p.page_size)) * p.G + g;
+      const uint32_t nbytes = ok ? 16u : 0u;
+      for (int c = piece; c < qv; c += 16)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(Kd + kk * ldk + c * 8)),
+                     "l"(kc + tok * dk + c * 8), "r"(nbytes) : "memory");
+      for (int c = piece; c < vv; c += 16)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(Vd + kk * ldv + c * 8)),
+                     "l"(vc + tok * dv + c * 8), "r"(nbytes) : "memory");
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
