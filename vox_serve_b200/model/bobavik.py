@@ -5,7 +5,7 @@ shared expert, with LayerNorm before and after every sublayer around an fp32 res
 design can vary (sizes, head counts, layer order, windows, decays, rotary constants, expert counts) is read from its
 ``config.json``; the arithmetic runs on ``HybridEngine`` (hybrid_engine.py).
 
-The adapter follows the same contract as the speech adapters (``BaseLM``) with ``is_text_model`` set: there is no audio
+The adapter has the same interface as the speech adapters (``BaseLM``) with ``is_text_model`` set: there is no audio
 codec, "detokenizing" a token means handing its id to the client, and the worker that serves it (worker/text.py) keeps a
 state slot per request next to the KV pages.
 
