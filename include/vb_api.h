@@ -469,7 +469,8 @@ int vb_codec_attn_chunk(float* d_out, const float* d_qkv, float* d_cache, int64_
  * dtype arguments: 0 = bf16, 1 = fp32.  Norm weights, router weights, decays and recurrent states are always fp32.
  * vb_embed_rows_f32:        out[t] = table[ids[t]] widened to fp32
  * vb_layernorm_f32:         out[t] = (x[r] - mean) / sqrt(var + eps) * w + b with r = rows ? rows[t] : t
- * vb_postnorm_residual_f32: x[t] += LN(y[t]; w1, b1); if out2: out2[t] = LN(x[t]; w2, b2)
+ * vb_postnorm_residual_f32: x[t] += LN(y[t]; w1, b1); if out2: out2[t] = LN(x[t]; w2, b2).  y [y_planes][T][width]: the fp32
+ *                           planes of a split-K projection are summed on the way in
  * vb_linear:                Y[r][n] = alpha * sum_k X[src(r)][k] W[g][n][k], fp32 accumulation in k order.  groups > 1:
  *                           group g owns rows row_off[g]..row_off[g+1] (T = upper bound of a group's rows), src(r) =
  *                           gather ? gather[r] : r.  epilogue 1: W = N gate rows then N up rows, Y = silu(gate) * up */
@@ -477,7 +478,7 @@ int vb_embed_rows_f32(float* d_out, const void* d_table, const int32_t* d_ids, i
                       void* stream);
 int vb_layernorm_f32(void* d_out, const float* d_x, const float* d_w, const float* d_b, const int32_t* d_rows, int T,
                      int width, float eps, int out_dtype, void* stream);
-int vb_postnorm_residual_f32(float* d_x, const float* d_y, const float* d_w1, const float* d_b1, void* d_out2,
+int vb_postnorm_residual_f32(float* d_x, const float* d_y, int y_planes, const float* d_w1, const float* d_b1, void* d_out2,
                              const float* d_w2, const float* d_b2, int T, int width, float eps, int out_dtype,
                              void* stream);
 int vb_linear(void* d_out, const void* d_x, const void* d_w, int T, int N, int K, int ldx, int ldo, int in_dtype,

@@ -105,7 +105,7 @@ SIGNATURES = {
     "vb_orpheus_window_codes": (c_int, [P, P, P, P, c_int, c_int, P]),
     "vb_embed_rows_f32": (c_int, [P, P, P, c_int, c_int, c_int, c_int, P]),
     "vb_layernorm_f32": (c_int, [P, P, P, P, P, c_int, c_int, c_float, c_int, P]),
-    "vb_postnorm_residual_f32": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_float, c_int, P]),
+    "vb_postnorm_residual_f32": (c_int, [P, P, c_int, P, P, P, P, P, c_int, c_int, c_float, c_int, P]),
     "vb_linear": (c_int, [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, P, P, c_int,
                           C.c_longlong, P]),
     "vb_cast_f32_bf16": (c_int, [P, P, C.c_longlong, P]),

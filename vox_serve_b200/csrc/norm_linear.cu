@@ -19,20 +19,18 @@ template <typename T> __device__ __forceinline__ T from_f(float v);
 template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
-__device__ __forceinline__ float block_sum(float v, float* red) {
-  // red: >= 33 floats of shared memory; every thread gets the total
+__device__ __forceinline__ float block_sum(float v, float* red, int& phase) {
+  // red: 64 floats of shared memory used as two alternating halves, so that one barrier per call is enough: a warp can only
+  // be one call ahead of the slowest warp, and then it writes the other half.  Every thread gets the total, summed in the
+  // same order by every warp.
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  float* r = red + 32 * (phase & 1);
+  ++phase;
   v = warp_sum(v);
+  if (lane == 0) r[w] = v;
   __syncthreads();
-  if (lane == 0) red[w] = v;
-  __syncthreads();
-  if (w == 0) {
-    float t = lane < nw ? red[lane] : 0.f;
-    t = warp_sum(t);
-    if (lane == 0) red[32] = t;
-  }
-  __syncthreads();
-  return red[32];
+  float t = lane < nw ? r[lane] : 0.f;
+  return warp_sum(t);
 }
 
 template <typename WT>
@@ -53,6 +51,7 @@ __global__ void layernorm_kernel(OT* __restrict__ out, const float* __restrict__
   extern __shared__ float sm[];
   float* row = sm;
   float* red = sm + W;
+  int phase = 0;
   pdl_sync();
   const int t = blockIdx.x;
   const size_t src = rows ? static_cast<size_t>(rows[t]) : static_cast<size_t>(t);
@@ -60,38 +59,46 @@ __global__ void layernorm_kernel(OT* __restrict__ out, const float* __restrict__
   __syncthreads();
   float s = 0.f;
   for (int i = threadIdx.x; i < W; i += blockDim.x) s += row[i];
-  const float mean = block_sum(s, red) / W;
+  const float mean = block_sum(s, red, phase) / W;
   float q = 0.f;
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
     const float d = row[i] - mean;
     q += d * d;
   }
-  const float rstd = 1.f / sqrtf(block_sum(q, red) / W + eps);
+  const float rstd = 1.f / sqrtf(block_sum(q, red, phase) / W + eps);
   for (int i = threadIdx.x; i < W; i += blockDim.x)
     out[static_cast<size_t>(t) * W + i] = from_f<OT>((row[i] - mean) * rstd * w[i] + b[i]);
 }
 
 // x[t] += LN(y[t]; w1, b1);  optionally out2[t] = LN(x[t]; w2, b2) (the pre-norm of the sublayer that follows)
+// (if (out2 == nullptr) return sits between two barriers of block_sum calls: it is uniform over the block)
 template <typename OT>
 __global__ void postnorm_residual_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ w1,
                                          const float* __restrict__ b1, OT* __restrict__ out2,
-                                         const float* __restrict__ w2, const float* __restrict__ b2, int W, float eps) {
+                                         const float* __restrict__ w2, const float* __restrict__ b2, int W, float eps,
+                                         int planes, long long plane_stride) {
   extern __shared__ float sm[];
   float* row = sm;
   float* red = sm + W;
+  int phase = 0;
   pdl_sync();
   const size_t t = blockIdx.x;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) row[i] = y[t * W + i];
+  // y may arrive as the fp32 planes of a split-K projection: they are summed here, in plane order
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float v = y[t * W + i];
+    for (int s = 1; s < planes; ++s) v += y[s * plane_stride + t * W + i];
+    row[i] = v;
+  }
   __syncthreads();
   float s = 0.f;
   for (int i = threadIdx.x; i < W; i += blockDim.x) s += row[i];
-  float mean = block_sum(s, red) / W;
+  float mean = block_sum(s, red, phase) / W;
   float q = 0.f;
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
     const float d = row[i] - mean;
     q += d * d;
   }
-  float rstd = 1.f / sqrtf(block_sum(q, red) / W + eps);
+  float rstd = 1.f / sqrtf(block_sum(q, red, phase) / W + eps);
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
     const float v = x[t * W + i] + ((row[i] - mean) * rstd * w1[i] + b1[i]);
     x[t * W + i] = v;
@@ -101,13 +108,13 @@ __global__ void postnorm_residual_kernel(float* __restrict__ x, const float* __r
   __syncthreads();
   s = 0.f;
   for (int i = threadIdx.x; i < W; i += blockDim.x) s += row[i];
-  mean = block_sum(s, red) / W;
+  mean = block_sum(s, red, phase) / W;
   q = 0.f;
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
     const float d = row[i] - mean;
     q += d * d;
   }
-  rstd = 1.f / sqrtf(block_sum(q, red) / W + eps);
+  rstd = 1.f / sqrtf(block_sum(q, red, phase) / W + eps);
   for (int i = threadIdx.x; i < W; i += blockDim.x)
     out2[t * W + i] = from_f<OT>((row[i] - mean) * rstd * w2[i] + b2[i]);
 }
@@ -265,7 +272,7 @@ int vb_layernorm_f32(void* d_out, const float* d_x, const float* d_w, const floa
                      int width, float eps, int out_dtype, void* stream) {
   VB_CHECK_ARG(d_out && d_x && d_w && d_b && width > 0, "vb_layernorm_f32: bad arguments");
   if (T <= 0) return 0;
-  const size_t smem = (static_cast<size_t>(width) + 40) * sizeof(float);
+  const size_t smem = (static_cast<size_t>(width) + 64) * sizeof(float);
   VB_CHECK_ARG(smem <= static_cast<size_t>(VB_MAX_DYN_SMEM), "vb_layernorm_f32: width %d too large", width);
   if (out_dtype == 1) {
     if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
@@ -277,20 +284,22 @@ int vb_layernorm_f32(void* d_out, const float* d_x, const float* d_w, const floa
   return 0;
 }
 
-int vb_postnorm_residual_f32(float* d_x, const float* d_y, const float* d_w1, const float* d_b1, void* d_out2,
+int vb_postnorm_residual_f32(float* d_x, const float* d_y, int y_planes, const float* d_w1, const float* d_b1, void* d_out2,
                              const float* d_w2, const float* d_b2, int T, int width, float eps, int out_dtype,
                              void* stream) {
+  VB_CHECK_ARG(y_planes >= 1, "vb_postnorm_residual_f32: planes");
+  const long long plane_stride = static_cast<long long>(T) * width;
   VB_CHECK_ARG(d_x && d_y && d_w1 && d_b1 && width > 0, "vb_postnorm_residual_f32: bad arguments");
   VB_CHECK_ARG(!d_out2 || (d_w2 && d_b2), "vb_postnorm_residual_f32: the second norm needs weight and bias");
   if (T <= 0) return 0;
-  const size_t smem = (static_cast<size_t>(width) + 40) * sizeof(float);
+  const size_t smem = (static_cast<size_t>(width) + 64) * sizeof(float);
   VB_CHECK_ARG(smem <= static_cast<size_t>(VB_MAX_DYN_SMEM), "vb_postnorm_residual_f32: width %d too large", width);
   if (out_dtype == 1) {
     if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(postnorm_residual_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
-    VB_LAUNCH_PDL(postnorm_residual_kernel<float>, T, 256, smem, stream, d_x, d_y, d_w1, d_b1, static_cast<float*>(d_out2), d_w2, d_b2, width, eps);
+    VB_LAUNCH_PDL(postnorm_residual_kernel<float>, T, 256, smem, stream, d_x, d_y, d_w1, d_b1, static_cast<float*>(d_out2), d_w2, d_b2, width, eps, y_planes, plane_stride);
   } else {
     if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(postnorm_residual_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
-    VB_LAUNCH_PDL(postnorm_residual_kernel<bf16>, T, 256, smem, stream, d_x, d_y, d_w1, d_b1, static_cast<bf16*>(d_out2), d_w2, d_b2, width, eps);
+    VB_LAUNCH_PDL(postnorm_residual_kernel<bf16>, T, 256, smem, stream, d_x, d_y, d_w1, d_b1, static_cast<bf16*>(d_out2), d_w2, d_b2, width, eps, y_planes, plane_stride);
   }
   return 0;
 }

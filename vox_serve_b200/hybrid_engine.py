@@ -367,8 +367,10 @@ class HybridEngine:
         self.use_tiled_attention = True
 
     # ---- projections -----------------------------------------------------------------------------------------
-    def _proj(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0) -> torch.Tensor:
-        """out (fp32) = alpha * x @ w^T: the tcgen05 kernel for packed bf16 weights, the fp32-FMA kernel otherwise."""
+    def _proj(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0, reduce: bool = True) -> torch.Tensor:
+        """out (fp32) = alpha * x @ w^T: the tcgen05 kernel for packed bf16 weights, the fp32-FMA kernel otherwise.
+        reduce=False: a split-K projection returns its partial planes [split, T, N] for a consumer that sums them (the
+        post-norm kernel can; measured slower than the separate, wider reduction at decode sizes, so it is not the default)."""
         if isinstance(w, ops.PackedWeight):
             assert alpha == 1.0 and out.dtype == F32 and out.is_contiguous()
             T = x.shape[0]
@@ -377,13 +379,13 @@ class HybridEngine:
             if split > 1 and split * T * w.N <= self.partials.numel():
                 planes = self.partials[:split * T * w.N].view(split, T, w.N)
                 ops.gemm(x, w, mode=1, split_k=split, out=planes)
-                return ops.sum_planes_f32(planes, out)
+                return ops.sum_planes_f32(planes, out) if reduce else planes
             ops.gemm(x, w, mode=1, split_k=1, out=out.view(1, T, w.N))
             return out
         return ops.linear(x, w, out, alpha=alpha)
 
     # ---- mixers ----------------------------------------------------------------------------------------------
-    def _attention(self, i: int, m: WindowAttentionConfig, w: Dict[str, Any], s: StepInputs) -> None:
+    def _attention(self, i: int, m: WindowAttentionConfig, w: Dict[str, Any], s: StepInputs) -> torch.Tensor:
         T, W = s.T, self.cfg.width
         nq, nk, nv = m.heads * m.dim, m.kv_heads * m.dim, m.kv_heads * m.vdim
         P = nq + nk + nv + m.heads * m.vdim
@@ -408,9 +410,9 @@ class HybridEngine:
             # decode rows (and mixed steps: single rows and portions together) on the warp-per-row kernel
             ops.window_attn(q, self.cache.k[i], self.cache.v[i], out, gate, s.row_req, s.pos, s.page_indptr, s.page_indices,
                             T, m.heads, m.kv_heads, m.dim, m.vdim, m.window, m.scale, scratch=self.attn_part)
-        self._proj(out, w["o"], self.y[:T])
+        return self._proj(out, w["o"], self.y[:T])
 
-    def _lightning(self, i: int, m: DecayAttentionConfig, w: Dict[str, Any], s: StepInputs) -> None:
+    def _lightning(self, i: int, m: DecayAttentionConfig, w: Dict[str, Any], s: StepInputs) -> torch.Tensor:
         T = s.T
         nq, nv = m.heads * m.dim, m.heads * m.vdim
         P = 2 * nq + 2 * nv
@@ -427,9 +429,9 @@ class HybridEngine:
                                  s.slots, s.tiles[0], s.tiles[1], s.tiles[2], s.B, m.heads, m.dim, m.vdim)
         out = self.mix_out[:T * nv].view(T, nv)
         ops.gated_rmsnorm(o, w["norm"], proj[:, 2 * nq + nv:], self.cfg.eps, out)
-        self._proj(out, w["o"], self.y[:T])
+        return self._proj(out, w["o"], self.y[:T])
 
-    def _moe(self, f: MoEConfig, w: Dict[str, Any], s: StepInputs) -> None:
+    def _moe(self, f: MoEConfig, w: Dict[str, Any], s: StepInputs) -> torch.Tensor:
         T, W = s.T, self.cfg.width
         h = self.h[:T]
         idx, wts = self.moe_idx[:T * f.top], self.moe_wts[:T * f.top]
@@ -439,8 +441,7 @@ class HybridEngine:
             act = self.moe_act[:T * n_all].view(T, n_all)
             ops.gemm(h, w["gu_all"], mode=2, out=act, tile_rows=w["gu_all"].tile_rows, n_out=n_all)
             ops.moe_scale_dense(act, idx, wts, f.experts, f.ff, f.top)
-            self._proj(act, w["down_all"], self.y[:T])
-            return
+            return self._proj(act, w["down_all"], self.y[:T])
         ops.moe_group(idx, T, f.experts, f.top, self.moe_row_off, self.moe_sorted, self.moe_pair_row)
         act = self.moe_act[:T * f.top * f.ff].view(T * f.top, f.ff)
         ops.linear(h, w["gu"], act, epilogue=1, row_off=self.moe_row_off, gather=self.moe_sorted, rows=T)
@@ -454,7 +455,7 @@ class HybridEngine:
             else:
                 ops.linear(h, w["s_gu"], sa, epilogue=1)
             shared = self._proj(sa, w["s_down"], self.s_out[:T])
-        ops.moe_combine(eo, shared, wts, self.moe_pair_row, f.top, self.y[:T])
+        return ops.moe_combine(eo, shared, wts, self.moe_pair_row, f.top, self.y[:T])
 
     # ---- the step --------------------------------------------------------------------------------------------
     def forward(self, s: StepInputs) -> torch.Tensor:
@@ -473,17 +474,18 @@ class HybridEngine:
             ops.layernorm_f32(x, *w.layers[0]["norm1"], eps, h)
         for i, L in enumerate(cfg.layers):
             lw = w.layers[i]
+            # (a sublayer hands back its output [T, W], or the split-K planes of its last projection [split, T, W])
             if L.kind == "attention":
-                self._attention(i, L.mixer, lw, s)
+                ym = self._attention(i, L.mixer, lw, s)
             else:
-                self._lightning(i, L.mixer, lw, s)
+                ym = self._lightning(i, L.mixer, lw, s)
             nxt = w.layers[i + 1]["norm1"] if i + 1 < n else None
             if L.mlp is not None:
-                ops.postnorm_residual_f32(x, y, *lw["norm1b"], eps, h, *lw["norm2"])
-                self._moe(L.mlp, lw, s)
-                ops.postnorm_residual_f32(x, y, *lw["norm2b"], eps, *((h,) + nxt if nxt else (None, None, None)))
+                ops.postnorm_residual_f32(x, ym, *lw["norm1b"], eps, h, *lw["norm2"])
+                yf = self._moe(L.mlp, lw, s)
+                ops.postnorm_residual_f32(x, yf, *lw["norm2b"], eps, *((h,) + nxt if nxt else (None, None, None)))
             else:
-                ops.postnorm_residual_f32(x, y, *lw["norm1b"], eps, *((h,) + nxt if nxt else (None, None, None)))
+                ops.postnorm_residual_f32(x, ym, *lw["norm1b"], eps, *((h,) + nxt if nxt else (None, None, None)))
             if self.layer_tap is not None:
                 self.layer_tap.append(x.clone())
         hn = self.hn[:s.n_out]

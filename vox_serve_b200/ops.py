@@ -944,10 +944,12 @@ def layernorm_f32(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, eps: float,
 def postnorm_residual_f32(x: torch.Tensor, y: torch.Tensor, w1: torch.Tensor, b1: torch.Tensor, eps: float,
                           out2: Optional[torch.Tensor] = None, w2: Optional[torch.Tensor] = None,
                           b2: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """x += LayerNorm(y; w1, b1) in place (fp32); with out2 also out2 = LayerNorm(x; w2, b2), bf16 or fp32."""
+    """x += LayerNorm(y; w1, b1) in place (fp32); with out2 also out2 = LayerNorm(x; w2, b2), bf16 or fp32.
+    y [T, W], or [planes, T, W]: the partial planes of a split-K projection, summed on the way in."""
     _need_cuda(x, y, w1, b1)
-    assert x.dtype == F32 and y.dtype == F32 and x.shape == y.shape and x.is_contiguous() and y.is_contiguous()
-    call("vb_postnorm_residual_f32", x.data_ptr(), y.data_ptr(), w1.data_ptr(), b1.data_ptr(), _p(out2), _p(w2), _p(b2),
+    planes = y.shape[0] if y.dim() == 3 else 1
+    assert x.dtype == F32 and y.dtype == F32 and tuple(x.shape) == tuple(y.shape[-2:]) and x.is_contiguous() and y.is_contiguous()
+    call("vb_postnorm_residual_f32", x.data_ptr(), y.data_ptr(), planes, w1.data_ptr(), b1.data_ptr(), _p(out2), _p(w2), _p(b2),
          x.shape[0], x.shape[1], float(eps), _dt(out2) if out2 is not None else 1, _stream())
     return x
 
