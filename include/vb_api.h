@@ -495,7 +495,8 @@ int vb_sum_planes_f32(float* d_out, const float* d_partials, int planes, long lo
  *                       row_req[t] (its pages are page_indices[page_indptr[b]..])
  * vb_window_attn:       out[t][h] = softmax over positions max(0, pos - window + 1)..pos of (q . k) * scale, times V, times
  *                       sigmoid(gate[t][h]) if gate; window <= 0 = no window.  d_part (optional, part_floats fp32): scratch
- *                       that lets steps of few rows split a row's keys over several CTAs.
+ *                       that lets steps of few rows split a row's keys over several CTAs.  d_row_list (optional): the T
+ *                       rows to serve (steps that run their prompt portions on the tiled kernel and the rest here).
  * vb_window_attn_tiled: the same result for prompt portions: tile i covers rows tile_row0[i].. (at most
  *                       vb_window_attn_tile_rows()) of request tile_req[i], whose rows are consecutive positions */
 int vb_rotary_table(float* d_cs, const int32_t* d_pos, const double* d_freq, int T, int half, void* stream);
@@ -506,7 +507,7 @@ int vb_qkv_rotary_append(const float* d_proj, int ldp, int q_off, int k_off, int
 int vb_window_attn(void* d_out, const void* d_q, const void* d_k_cache, const void* d_v_cache, const float* d_gate,
                    int ld_gate, const int32_t* d_row_req, const int32_t* d_pos, const int32_t* d_page_indptr,
                    const int32_t* d_page_indices, int T, int H, int G, int dim, int vdim, int page_size, int window,
-                   float scale, int dtype, float* d_part, long long part_floats, void* stream);
+                   float scale, int dtype, float* d_part, long long part_floats, const int32_t* d_row_list, void* stream);
 int vb_window_attn_tile_rows(void);
 int vb_window_attn_tiled(void* d_out, const void* d_q, const void* d_k_cache, const void* d_v_cache, const float* d_gate,
                          int ld_gate, const int32_t* d_pos, const int32_t* d_page_indptr, const int32_t* d_page_indices,

@@ -115,6 +115,7 @@ struct WindowAttnParams {
   const int32_t* tile_row0;   // tiled kernel: first row of tile i
   int T, H, G, dim, vdim, page_size, window;   // window <= 0: every earlier position is visible
   float scale;
+  const int32_t* row_list;    // per-row kernels: the rows to serve (nullptr: rows 0 .. T - 1); T counts the served rows
   int splits;                 // grouped kernel: key tiles are dealt round-robin to `splits` CTAs per (row, key/value head)
   float* part;                // [T][H][splits][vdim + 2]: unnormalised output, running max, running sum of every split
 };
@@ -200,8 +201,9 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attn_kernel(WindowAttnPa
   extern __shared__ float smf[];
   pdl_sync();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * WA_WARPS + warp, h = blockIdx.y;
-  if (t >= p.T) return;
+  const int ti = blockIdx.x * WA_WARPS + warp, h = blockIdx.y;
+  if (ti >= p.T) return;
+  const int t = p.row_list ? p.row_list[ti] : ti;
   float* qs = smf + warp * p.dim;
   const CT* q = static_cast<const CT*>(p.q) + (static_cast<size_t>(t) * p.H + h) * p.dim;
   for (int d = lane; d < p.dim; d += 32) qs[d] = wa_to_f(q[d]) * p.scale;
@@ -374,7 +376,8 @@ template <typename CT>
 __global__ void __launch_bounds__(128) window_attn_group_kernel(WindowAttnParams p) {
   extern __shared__ float smf[];
   pdl_sync();
-  const int t = blockIdx.x, g = blockIdx.y, R = p.H / p.G;
+  const int ti = blockIdx.x, g = blockIdx.y, R = p.H / p.G;
+  const int t = p.row_list ? p.row_list[ti] : ti;
   const int dk = p.dim, dv = p.vdim, dkp = dk + 1, dvp = dv + 1;
   float* Qs = smf;                      // [R][dk]
   float* Ks = Qs + R * dk;              // [32][dk + 1]
@@ -440,7 +443,7 @@ __global__ void __launch_bounds__(128) window_attn_group_kernel(WindowAttnParams
     if (r >= R) break;
     const int h = g * R + r;
     if (S > 1) {              // leave this split's share for vb::window_attn_merge_kernel
-      float* pt = p.part + ((static_cast<size_t>(t) * p.H + h) * S + sidx) * (dv + 2);
+      float* pt = p.part + ((static_cast<size_t>(ti) * p.H + h) * S + sidx) * (dv + 2);
 #pragma unroll
       for (int v = 0; v < WD_VU; ++v) {
         const int d = lane + 32 * v;
@@ -471,8 +474,9 @@ __global__ void __launch_bounds__(128) window_attn_group_kernel(WindowAttnParams
 template <typename CT>
 __global__ void __launch_bounds__(64) window_attn_merge_kernel(WindowAttnParams p) {
   pdl_sync();
-  const int t = blockIdx.x, h = blockIdx.y, S = p.splits, dv = p.vdim;
-  const float* pt = p.part + (static_cast<size_t>(t) * p.H + h) * S * (dv + 2);
+  const int ti = blockIdx.x, h = blockIdx.y, S = p.splits, dv = p.vdim;
+  const int t = p.row_list ? p.row_list[ti] : ti;
+  const float* pt = p.part + (static_cast<size_t>(ti) * p.H + h) * S * (dv + 2);
   float M = -INFINITY;
   for (int s = 0; s < S; ++s) M = fmaxf(M, pt[s * (dv + 2) + dv]);
   float L = 0.f;
@@ -713,14 +717,14 @@ int vb_qkv_rotary_append(const float* d_proj, int ldp, int q_off, int k_off, int
 int vb_window_attn(void* d_out, const void* d_q, const void* d_k_cache, const void* d_v_cache, const float* d_gate,
                    int ld_gate, const int32_t* d_row_req, const int32_t* d_pos, const int32_t* d_page_indptr,
                    const int32_t* d_page_indices, int T, int H, int G, int dim, int vdim, int page_size, int window,
-                   float scale, int dtype, float* d_part, long long part_floats, void* stream) {
+                   float scale, int dtype, float* d_part, long long part_floats, const int32_t* d_row_list, void* stream) {
   VB_CHECK_ARG(d_out && d_q && d_k_cache && d_v_cache && d_row_req && d_pos && d_page_indptr && d_page_indices,
                "vb_window_attn: null pointer");
   VB_CHECK_ARG(H > 0 && G > 0 && H % G == 0 && dim > 0 && vdim > 0 && vdim <= 32 * WA_MAXU && page_size > 0,
                "vb_window_attn: bad sizes H=%d G=%d dim=%d vdim=%d (vdim <= %d)", H, G, dim, vdim, 32 * WA_MAXU);
   if (T <= 0) return 0;
   WindowAttnParams p{d_q, d_k_cache, d_v_cache, d_out, d_gate, ld_gate, d_row_req, d_pos, d_page_indptr, d_page_indices,
-                     nullptr, nullptr, nullptr, T, H, G, dim, vdim, page_size, window, scale, 1, d_part};
+                     nullptr, nullptr, nullptr, T, H, G, dim, vdim, page_size, window, scale, d_row_list, 1, d_part};
   // a CTA per (row, key/value head) with the K / V tiles shared by the group's query heads, when the group fits its
   // registers and the tiles fit shared memory; one warp per (row, query head) otherwise
   const int R = H / G;
@@ -768,7 +772,7 @@ int vb_window_attn_tiled(void* d_out, const void* d_q, const void* d_k_cache, co
                "vb_window_attn_tiled: bad sizes H=%d G=%d dim=%d vdim=%d", H, G, dim, vdim);
   if (n_tiles <= 0) return 0;
   WindowAttnParams p{d_q, d_k_cache, d_v_cache, d_out, d_gate, ld_gate, nullptr, d_pos, d_page_indptr, d_page_indices,
-                     d_qo_indptr, d_tile_req, d_tile_row0, T, H, G, dim, vdim, page_size, window, scale, 1, nullptr};
+                     d_qo_indptr, d_tile_req, d_tile_row0, T, H, G, dim, vdim, page_size, window, scale, nullptr, 1, nullptr};
   dim3 grid(n_tiles, H);
   if (dtype == 0 && dim % 16 == 0 && vdim % 16 == 0 && dim <= 16 * F_KB && vdim <= 8 * F_NT) {
     const size_t msmem = 2 * static_cast<size_t>(FN) * (dim + 8 + vdim + 8) * sizeof(__nv_bfloat16);      // two stages

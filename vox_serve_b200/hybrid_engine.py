@@ -290,7 +290,8 @@ class StepInputs:
     """Device-side description of one step (all int32): ``ids`` / ``pos`` / ``row_req`` per token row, ``qo_indptr``
     [B + 1] rows of every request, ``page_indptr`` [B + 1] + ``page_indices`` its pages, ``slots`` [B] its state slot,
     ``out_rows`` the rows whose logits are computed.  ``multi`` / ``single``: whether any request brings more than one /
-    exactly one token (host knowledge: selects the prompt-portion and the single-token kernels).  ``tiles``: row tiles
+    exactly one token (host knowledge: selects the prompt-portion and the single-token kernels; ``single_rows`` lists the latter's
+    rows for steps that have both).  ``tiles``: row tiles
     (tile_req, tile_row0, n_tiles) of the requests that bring several tokens, for the tiled attention kernel."""
     ids: torch.Tensor
     pos: torch.Tensor
@@ -306,6 +307,7 @@ class StepInputs:
     multi: bool = True
     single: bool = True
     tiles: Optional[Tuple[torch.Tensor, torch.Tensor, int]] = None
+    single_rows: Optional[Tuple[torch.Tensor, int]] = None      # the rows of the requests that bring exactly one token
 
 
 class HybridEngine:
@@ -403,13 +405,16 @@ class HybridEngine:
         tiles = None
         if s.tiles is not None and self.use_tiled_attention and m.vdim <= 256:
             tiles = (s.qo_indptr, s.tiles[0], s.tiles[1], s.tiles[2])
-        if tiles is not None and not s.single:
-            ops.window_attn(q, self.cache.k[i], self.cache.v[i], out, gate, s.row_req, s.pos, s.page_indptr, s.page_indices,
-                            T, m.heads, m.kv_heads, m.dim, m.vdim, m.window, m.scale, tiles=tiles)
+        args = (q, self.cache.k[i], self.cache.v[i], out, gate, s.row_req, s.pos, s.page_indptr, s.page_indices, T, m.heads,
+                m.kv_heads, m.dim, m.vdim, m.window, m.scale)
+        if tiles is not None and (not s.single or s.single_rows is not None):
+            # prompt portions on the tiled kernel; in a mixed step the single-token rows on the per-row kernel
+            ops.window_attn(*args, tiles=tiles)
+            if s.single:
+                ops.window_attn(*args, scratch=self.attn_part, rows=s.single_rows)
         else:
-            # decode rows (and mixed steps: single rows and portions together) on the warp-per-row kernel
-            ops.window_attn(q, self.cache.k[i], self.cache.v[i], out, gate, s.row_req, s.pos, s.page_indptr, s.page_indices,
-                            T, m.heads, m.kv_heads, m.dim, m.vdim, m.window, m.scale, scratch=self.attn_part)
+            # decode steps (and steps without tiles) on the per-row kernel
+            ops.window_attn(*args, scratch=self.attn_part)
         return self._proj(out, w["o"], self.y[:T])
 
     def _lightning(self, i: int, m: DecayAttentionConfig, w: Dict[str, Any], s: StepInputs) -> torch.Tensor:

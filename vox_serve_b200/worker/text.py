@@ -44,7 +44,7 @@ class TextModelWorker(CudaGraphWorker):
         self.max_tiles = self.max_rows // self.tile_rows + B + 1
         self.staging = _Staging(B, self.max_rows, self.max_num_pages, dev,
                                 extra=(("row_req", self.max_rows), ("out_rows", B + self.max_logit_rows),
-                                       ("tile_req", self.max_tiles), ("tile_row0", self.max_tiles)))
+                                       ("tile_req", self.max_tiles), ("tile_row0", self.max_tiles), ("single_rows", B)))
         self.free_slots = list(range(B - 1, -1, -1))
         self.slot_of: Dict[str, int] = {}
         cfg = m.default_sampling_config
@@ -66,7 +66,7 @@ class TextModelWorker(CudaGraphWorker):
         self.use_cuda_graph = True
         self.gpu_launches = 0
         self._graph_nodes: Dict[int, int] = {}
-        self._step_meta = (0, False, False, 0)       # (logit rows, any portion, any single row, tiles) of the staged step
+        self._step_meta = (0, False, False, 0, 0)    # (logit rows, any portion, any single row, tiles, single rows) of the staged step
         self._logit_index: Dict[str, List[int]] = {}
         self.prefill_wrapper = self.decode_wrapper = None
 
@@ -91,6 +91,7 @@ class TextModelWorker(CudaGraphWorker):
         qo, ip, slots = st.h("qo"), st.h("indptr"), st.h("slots")
         pos, ids, row_slot, indices = st.h("pos"), st.h("ids"), st.h("row_slot"), st.h("indices")
         row_req, out_rows, tile_req, tile_row0 = st.h("row_req"), st.h("out_rows"), st.h("tile_req"), st.h("tile_row0")
+        single_rows = st.h("single_rows")
         # ---- what every request brings ----
         plan = []           # (request, number of rows, ids or None)
         failed: List[Request] = []
@@ -136,7 +137,7 @@ class TextModelWorker(CudaGraphWorker):
                 return None
         # ---- the packed tables ----
         B = len(plan)
-        t = npg = n_tiles = 0
+        t = npg = n_tiles = n_single = 0
         extra = B                     # logit rows: the last row of every request first, tapped rows after them
         qo[0] = ip[0] = 0
         any_multi = any_single = False
@@ -160,6 +161,8 @@ class TextModelWorker(CudaGraphWorker):
                     n_tiles += 1
             else:
                 any_single = True
+                single_rows[n_single] = t
+                n_single += 1
             out_rows[b] = t + n - 1
             idx = []
             for r in (req.logit_rows or []):
@@ -185,7 +188,7 @@ class TextModelWorker(CudaGraphWorker):
             npg += k
             t += n
             qo[b + 1], ip[b + 1], slots[b] = t, npg, slot
-        self._step_meta = (extra, any_multi, any_single, n_tiles)
+        self._step_meta = (extra, any_multi, any_single, n_tiles, n_single)
         lm_inputs = {"qo_indptr": qo[:B + 1].tolist(), "paged_kv_indptr": ip[:B + 1].tolist(),
                      "paged_kv_indices": indices[:npg].tolist(),
                      "paged_kv_last_page_len": [r.kv_last_page_len for r, _, _ in plan],
@@ -200,14 +203,15 @@ class TextModelWorker(CudaGraphWorker):
     def _device_step(self, B: int, T: int, is_prefill: bool):
         st, m = self.staging, self.model
         if is_prefill:
-            n_out, multi, single, n_tiles = self._step_meta
+            n_out, multi, single, n_tiles, n_single = self._step_meta
         else:                                            # (also what a decode graph captures: one row per request)
-            n_out, multi, single, n_tiles = B, False, True, 0
+            n_out, multi, single, n_tiles, n_single = B, False, True, 0, 0
         ops.build_input_ids(self.input_ids, st.d("ids"), self.next_input, st.d("row_slot"), T)
         step = StepInputs(ids=self.input_ids[:T], pos=st.d("pos", T), row_req=st.d("row_req", T), qo_indptr=st.d("qo", B + 1),
                           page_indptr=st.d("indptr", B + 1), page_indices=st.d("indices"), slots=st.d("slots", B),
                           out_rows=st.d("out_rows", n_out), B=B, T=T, n_out=n_out, multi=multi, single=single,
-                          tiles=(st.d("tile_req"), st.d("tile_row0"), n_tiles) if n_tiles else None)
+                          tiles=(st.d("tile_req"), st.d("tile_row0"), n_tiles) if n_tiles else None,
+                          single_rows=(st.d("single_rows"), n_single) if (n_tiles and n_single) else None)
         logits = m.forward(step, engine=self.engine)
         slots = st.d("slots", B)
         out = self.out_ids[:B]
