@@ -284,13 +284,15 @@ __global__ void __launch_bounds__(256) decay_tile_out_kernel(DecayTileParams tp)
   const int b = tp.tile_req[tile], row0 = tp.tile_row0[tile];
   const int L = min(DT_ROWS, p.qo_indptr[b + 1] - row0);
   constexpr int C = DT_ROWS;
-  const int dk = p.dim, dkp = dk + 1, DV = min(p.dvb, p.vdim - e0), dvp = p.dvb + 1;
-  float* Sq = smf;                    // [C][dk + 1]
-  float* Sk = Sq + C * dkp;           // [C][dk + 1]
-  float* Sv = Sk + C * dkp;           // [C][dvb + 1]
-  float* Sa = Sv + C * dvp;           // [C][C + 1]
-  float* Ss = Sa + C * (C + 1);       // [dk][dvb + 1]
-  float* pw = Ss + dk * dvp;          // [C + 1]
+  // shared memory is laid out for two CTAs per SM at 128-wide heads: the scores overwrite the key tile once it has been
+  // consumed, and the value / state tiles (read along the value dim only) carry no padding
+  const int dk = p.dim, dkp = dk + 1, DV = min(p.dvb, p.vdim - e0), dvp = p.dvb;
+  float* Sq = smf;                                   // [C][dk + 1]
+  float* Sk = Sq + C * dkp;                          // [C][dk + 1], then the scores [C][C + 1]
+  float* Sa = Sk;
+  float* Sv = Sk + C * max(dkp, C + 1);              // [C][dvb]
+  float* Ss = Sv + C * dvp;                          // [dk][dvb]
+  float* pw = Ss + dk * dvp;                         // [C + 1]
   const int tid = threadIdx.x;
   const double d = static_cast<double>(p.decay[h]);
   for (int i = tid; i <= C; i += 256) pw[i] = static_cast<float>(pow(d, static_cast<double>(i)));
@@ -334,6 +336,7 @@ __global__ void __launch_bounds__(256) decay_tile_out_kernel(DecayTileParams tp)
 #pragma unroll
         for (int j = 0; j < 4; ++j) a[i][j] = fmaf(qv[i], kv[j], a[i][j]);
     }
+    __syncthreads();                                 // the key tile is consumed: its place takes the scores
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -486,7 +489,8 @@ int vb_decay_attn_tiled(float* d_out, float* d_state, float* d_scratch, const fl
                       dvb, DT_ROWS, 2, 1 << 30}, d_scratch, d_tile_req, d_tile_row0, B};
   const int zb = (vdim + dvb - 1) / dvb;
   const size_t smem1 = (static_cast<size_t>(DT_ROWS) * (dim + 1 + dvb + 1) + DT_ROWS + 1) * sizeof(float);
-  const size_t smem3 = chunked_smem(DT_ROWS, dim, dvb);
+  const size_t smem3 = (static_cast<size_t>(DT_ROWS) * (dim + 1) + static_cast<size_t>(DT_ROWS) * max(dim + 1, DT_ROWS + 1) +
+                        static_cast<size_t>(DT_ROWS) * dvb + static_cast<size_t>(dim) * dvb + DT_ROWS + 1) * sizeof(float);
   VB_CHECK_CUDA(cudaFuncSetAttribute(decay_tile_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
   VB_CHECK_CUDA(cudaFuncSetAttribute(decay_tile_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
   VB_LAUNCH_PDL(decay_tile_state_kernel, dim3(n_tiles, H, zb), 256, smem1, stream, tp);

@@ -504,7 +504,9 @@ constexpr int FM = 64, FN = 64, F_KB = 8, F_NT = 16;      // dim <= 16 * F_KB, v
 __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnParams p) {
   extern __shared__ __align__(16) uint8_t smraw[];
   pdl_sync();
-  const int b = p.tile_req[blockIdx.x], row0 = p.tile_row0[blockIdx.x], h = blockIdx.y;
+  // later tiles of a prompt see more keys: they are started first so that the short ones fill the tail
+  const int tile = gridDim.x - 1 - blockIdx.x;
+  const int b = p.tile_req[tile], row0 = p.tile_row0[tile], h = blockIdx.y;
   const int nrows = min(row0 + FM, p.qo_indptr[b + 1]) - row0;
   const int dk = p.dim, dv = p.vdim, ldk = dk + 8, ldv = dv + 8, nkb = dk / 16, nvp = dv / 16;
   // two stages of K [64][dk + 8] | V [64][dv + 8]; the first stage's K region holds the Q tile first
