@@ -465,6 +465,15 @@ int vb_codec_rmsnorm(float* d_y, const float* d_x, const float* d_w, int B, int 
 int vb_codec_attn_chunk(float* d_out, const float* d_qkv, float* d_cache, int64_t cache_batch_stride, const int64_t* d_pos0,
                         int B, int H, int Hkv, int D, int T, int W, float theta, void* stream);
 
+/* vb_gemm_bf16 with grouped weights (mixture of experts): the rows of token tile i (t_tile rows; x row-major through
+ * x_map whose box is t_tile rows) multiply the weights of group d_tile_group[i] (NULL: group 0).  Group g's matrix lies
+ * group_bytes * g further in d_w_tiles (matrices stacked along N) and / or its k-blocks lie group_kb * g + kb_base further
+ * inside rows of w_kb_stride k-blocks (matrices stacked along K; 0 = ceil(K / 64)).  mode 1: fp32 [T][ldy]; mode 2:
+ * silu(gate) * up, bf16 [T][ldy]. */
+int vb_gemm_bf16_grouped(void* d_y, const void* d_w_tiles, const void* x_map, int T, int N, int K, int ldy, int mode,
+                         int tile_rows, int n_out, int t_tile, const int32_t* d_tile_group, long long group_bytes,
+                         int w_kb_stride, int group_kb, int kb_base, void* stream);
+
 /* ---- hybrid decoder stacks with an fp32 residual stream (norm_linear.cu, window_attn.cu, linear_attn.cu, moe.cu) ----
  * dtype arguments: 0 = bf16, 1 = fp32.  Norm weights, router weights, decays and recurrent states are always fp32.
  * vb_embed_rows_f32:        out[t] = table[ids[t]] widened to fp32
@@ -535,7 +544,11 @@ int vb_gated_rmsnorm(void* d_out, const float* d_x, const float* d_w, const floa
 int vb_moe_route(int32_t* d_idx, float* d_wts, const void* d_h, const float* d_router_w, const float* d_router_b, int T,
                  int width, int experts, int top, int h_dtype, void* stream);
 int vb_moe_group(int32_t* d_row_off, int32_t* d_sorted_token, int32_t* d_pair_row, const int32_t* d_idx, int T,
-                 int experts, int top, void* stream);
+                 int experts, int top, int tile_rows, int32_t* d_tile_group, int n_tiles, void* stream);
+/* (tile_rows > 0: every expert's rows start at a multiple of tile_rows; padding rows get token -1; d_tile_group[i] =
+ * the expert of row tile i, 0 for tiles past the last expert, i < n_tiles >= ceil(T * top / tile_rows) + experts)
+ * vb_moe_gather_rows: out[r] = token[r] >= 0 ? x[token[r]] : 0, bf16 rows of `width` (a multiple of 8) */
+int vb_moe_gather_rows(void* d_out, const void* d_x, const int32_t* d_token, int rows, int width, void* stream);
 /* dense form (bf16): act [T][ld] holds silu(gate) * up of EVERY expert side by side (expert e at columns e * ff ..), then
  * the shared expert's; columns of expert e are scaled by the token's routing weight for e, or zeroed if e was not chosen */
 int vb_moe_scale_dense(void* d_act, const int32_t* d_idx, const float* d_wts, int T, int ld, int experts, int ff, int top,

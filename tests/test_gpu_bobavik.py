@@ -243,6 +243,23 @@ def test_prefill_decode_portions_and_batches(dtype):
 
 
 @pytest.mark.gpu
+def test_grouped_experts_on_long_prompts():
+    """bfloat16 steps of 512 rows or more sort their tokens by expert and run whole row tiles per expert; shorter steps run
+    every expert on every token and zero what was not chosen.  Both against the oracle, and against each other."""
+    cfg = O.make_config(width=64, layers=("attention", "lightning"), ff=64, shared_ff=96, experts=4, top=2, dim=16, vdim=16,
+                        window=40)
+    sd = O.random_weights(cfg, 23)
+    toks = _tokens(700, cfg["vocab"], 9)
+    ref = O.forward(cfg, sd, toks)
+    w = _worker(cfg, sd, BF16, pages=100, page_size=8, max_rows=768)
+    assert "grouped" in w.engine.w.layers[0] and w.engine.GROUPED_MIN_ROWS <= 700
+    whole = _replay(w, {"a": toks}, [[("a", 700)]])["a"]
+    parts = _replay(w, {"a": toks}, [[("a", 175)]] * 4)["a"]
+    assert _err(whole, ref) < TOL[BF16] and _err(parts, ref) < TOL[BF16]
+    assert _err(whole, parts.double()) < TOL[BF16]
+
+
+@pytest.mark.gpu
 def test_long_decoding_past_window_and_pages():
     cfg = O.make_config(layers=("lightning", "attention"), window=20, decay=(0.99, 0.7))
     sd = O.random_weights(cfg, 9)

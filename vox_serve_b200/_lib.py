@@ -125,7 +125,10 @@ SIGNATURES = {
                                     c_int, P]),
     "vb_gated_rmsnorm": (c_int, [P, P, P, P, c_int, c_int, c_int, c_float, c_int, P]),
     "vb_moe_route": (c_int, [P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P]),
-    "vb_moe_group": (c_int, [P, P, P, P, c_int, c_int, c_int, P]),
+    "vb_moe_group": (c_int, [P, P, P, P, c_int, c_int, c_int, c_int, P, c_int, P]),
+    "vb_moe_gather_rows": (c_int, [P, P, P, c_int, c_int, P]),
+    "vb_gemm_bf16_grouped": (c_int, [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, C.c_longlong,
+                                     c_int, c_int, c_int, P]),
     "vb_moe_combine": (c_int, [P, P, P, P, P, c_int, c_int, c_int, P]),
     "vb_moe_scale_dense": (c_int, [P, P, P, c_int, c_int, c_int, c_int, c_int, P]),
 }

@@ -63,6 +63,13 @@ struct GemmParams {
   int n_q, n_kv, page_size;
   // mode 0: optional bias [N] added in fp32 before the single bf16 rounding (nn.Linear with bias)
   const __nv_bfloat16* bias;
+  // grouped weights (mixture of experts): token tile t_blk multiplies the weights of group tile_group[t_blk] (nullptr:
+  // group 0).  A group's matrix starts group_bytes after the previous one (matrices stacked along N), and / or its k-blocks
+  // start group_kb after the previous one's inside rows of w_kb_stride k-blocks (matrices stacked along K; 0: the
+  // problem's own k-block count); kb_base: a constant k-block offset.
+  const int32_t* tile_group;
+  long long group_bytes;
+  int w_kb_stride, group_kb, kb_base;
 };
 
 __device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -152,7 +159,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2) gemm_bf16_kernel(const GemmPa
       // still running, then wait for it and add the activation tiles to the same stages.
       // A (tile, k-block) weight tile is one contiguous, pre-swizzled a_stage-byte run in HBM and this CTA's
       // k-blocks follow each other: a single linear bulk copy per stage, sequential DRAM bursts.
-      const uint8_t* wsrc = p.w_tiles + (static_cast<size_t>(n_tile) * num_kb + kb0) * a_stage;
+      const int grp = p.tile_group ? p.tile_group[t_blk] : 0;
+      const size_t w_kbs = p.w_kb_stride ? p.w_kb_stride : num_kb;
+      const uint8_t* wsrc = p.w_tiles + static_cast<size_t>(grp) * p.group_bytes +
+                            (static_cast<size_t>(n_tile) * w_kbs + static_cast<size_t>(grp) * p.group_kb + p.kb_base + kb0) * a_stage;
       const int npre = min(p.stages, kb1 - kb0);
       for (int i = 0; i < npre; ++i) {
         mbar_arrive_expect_tx(&full[i], stage_bytes);
@@ -705,6 +715,23 @@ int vb_gemm_bf16(void* d_y, const void* d_w_tiles, const void* x_map, const void
   p.y_tiled = y_tiled;
   p.bias = static_cast<const __nv_bfloat16*>(d_bias);
   return launch_gemm(p, d_w_tiles, x_map, static_cast<cudaStream_t>(stream), d_x_tiles);
+}
+
+int vb_gemm_bf16_grouped(void* d_y, const void* d_w_tiles, const void* x_map, int T, int N, int K, int ldy, int mode,
+                         int tile_rows, int n_out, int t_tile, const int32_t* d_tile_group, long long group_bytes,
+                         int w_kb_stride, int group_kb, int kb_base, void* stream) {
+  VB_CHECK_ARG(d_y && d_w_tiles && x_map, "vb_gemm_bf16_grouped: null pointer");
+  VB_CHECK_ARG(mode == 1 || mode == 2, "vb_gemm_bf16_grouped: mode %d (1: fp32 out, 2: silu(gate) * up)", mode);
+  VB_CHECK_ARG(mode != 2 || (tile_rows % 32 == 0 && N % tile_rows == 0), "vb_gemm_bf16_grouped: mode 2 tile_rows");
+  VB_CHECK_ARG(t_tile >= 16 && t_tile <= 256 && t_tile % 16 == 0, "vb_gemm_bf16_grouped: t_tile %d", t_tile);
+  VB_CHECK_ARG(group_bytes >= 0 && w_kb_stride >= 0 && group_kb >= 0 && kb_base >= 0, "vb_gemm_bf16_grouped: offsets");
+  GemmParams p = {};
+  p.y = d_y; p.T = T; p.N = N; p.K = K; p.ldy = ldy; p.mode = mode; p.split_k = 1;
+  p.tile_rows = tile_rows > 0 ? tile_rows : 128;
+  p.n_out = n_out > 0 ? n_out : (mode == 2 ? N / 2 : N);
+  p.t_tile = t_tile;
+  p.tile_group = d_tile_group; p.group_bytes = group_bytes; p.w_kb_stride = w_kb_stride; p.group_kb = group_kb; p.kb_base = kb_base;
+  return launch_gemm(p, d_w_tiles, x_map, static_cast<cudaStream_t>(stream), nullptr);
 }
 
 size_t vb_norm_lmhead_workspace_bytes(int T, int K) {

@@ -2,7 +2,7 @@
 // of vb_linear):
 //   vb_moe_route    router logits z = W_r h + b in fp32 (h bf16 or fp32), the `top` largest per token (ties: the lower
 //                   expert index), weights = softmax over the chosen logits only
-//   vb_moe_group    counting sort of the (token, choice) pairs by expert: row_off[E + 1], the token of every sorted row and
+//   vb_moe_group    counting sort (shared-memory counters, one CTA) of the (token, choice) pairs by expert: row_off[E + 1], the token of every sorted row and
 //                   the sorted row of every (token, choice)
 //   vb_moe_scale_dense  the dense form for tensor-core projections: every expert runs on every token as ONE stacked
 //                   gate/up projection [E * ff (+ shared ff)] and ONE stacked down projection over that whole axis; in
@@ -80,7 +80,8 @@ __global__ void __launch_bounds__(256) moe_route_kernel(int32_t* __restrict__ id
 // single CTA: E <= 1024 experts, any number of pairs
 __global__ void __launch_bounds__(1024) moe_group_kernel(int32_t* __restrict__ row_off, int32_t* __restrict__ sorted_token,
                                                          int32_t* __restrict__ pair_row, const int32_t* __restrict__ idx,
-                                                         int T, int E, int top) {
+                                                         int T, int E, int top, int tile_rows,
+                                                         int32_t* __restrict__ tile_group, int n_tiles) {
   __shared__ int cnt[1024];
   __shared__ int base[1025];
   pdl_sync();
@@ -91,22 +92,35 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(int32_t* __restrict__ r
   __syncthreads();
   if (tid == 0) {
     int s = 0;
-    for (int e = 0; e < E; ++e) { base[e] = s; s += cnt[e]; }
+    for (int e = 0; e < E; ++e) {
+      base[e] = s;
+      s += tile_rows > 0 ? (cnt[e] + tile_rows - 1) / tile_rows * tile_rows : cnt[e];
+    }
     base[E] = s;
   }
   __syncthreads();
   for (int e = tid; e <= E; e += 1024) row_off[e] = base[e];
-  // rows of an expert in token order: every expert's rows are placed by one thread walking the pairs in order
-  // (deterministic placement; E threads share the scan of n pairs)
-  for (int e = tid; e < E; e += 1024) {
-    int r = base[e];
-    if (cnt[e] == 0) continue;
-    for (int i = 0; i < n; ++i)
-      if (idx[i] == e) {
-        sorted_token[r] = i / top;
-        pair_row[i] = r;
-        ++r;
-      }
+  if (tile_rows > 0) {
+    // padded layout: rows that hold no pair read as token -1; every row tile belongs to one expert
+    for (int r = tid; r < n_tiles * tile_rows; r += 1024) sorted_token[r] = -1;
+    for (int i = tid; i < n_tiles; i += 1024) {
+      int g = 0;
+      for (int e = 0; e < E; ++e)
+        if (i * tile_rows >= base[e] && i * tile_rows < base[e + 1]) g = e;
+      tile_group[i] = g;
+    }
+    __syncthreads();
+  }
+  // placement: a pair takes the next free row of its expert.  The order of an expert's rows varies from run to run; every
+  // row is computed on its own and found again through pair_row, so results do not depend on it.
+  __syncthreads();
+  for (int e = tid; e < E; e += 1024) cnt[e] = 0;
+  __syncthreads();
+  for (int i = tid; i < n; i += 1024) {
+    const int e = idx[i];
+    const int r = base[e] + atomicAdd(&cnt[e], 1);
+    sorted_token[r] = i / top;
+    pair_row[i] = r;
   }
 }
 
@@ -141,6 +155,15 @@ __global__ void moe_scale_dense_kernel(__nv_bfloat16* __restrict__ act, const in
   }
 }
 
+__global__ void moe_gather_rows_kernel(uint4* __restrict__ out, const uint4* __restrict__ x, const int32_t* __restrict__ token,
+                                       int vecs) {
+  pdl_sync();
+  const size_t r = blockIdx.x;
+  const int t = token[r];
+  for (int i = threadIdx.x; i < vecs; i += blockDim.x)
+    out[r * vecs + i] = t >= 0 ? x[static_cast<size_t>(t) * vecs + i] : make_uint4(0u, 0u, 0u, 0u);
+}
+
 }  // namespace vb
 
 using namespace vb;
@@ -161,11 +184,22 @@ int vb_moe_route(int32_t* d_idx, float* d_wts, const void* d_h, const float* d_r
 }
 
 int vb_moe_group(int32_t* d_row_off, int32_t* d_sorted_token, int32_t* d_pair_row, const int32_t* d_idx, int T,
-                 int experts, int top, void* stream) {
+                 int experts, int top, int tile_rows, int32_t* d_tile_group, int n_tiles, void* stream) {
   VB_CHECK_ARG(d_row_off && d_sorted_token && d_pair_row && d_idx, "vb_moe_group: null pointer");
   VB_CHECK_ARG(experts >= 1 && experts <= 1024, "vb_moe_group: experts %d (<= 1024)", experts);
+  VB_CHECK_ARG(tile_rows == 0 || (d_tile_group && n_tiles >= (T * top + tile_rows - 1) / tile_rows + experts),
+               "vb_moe_group: the padded layout needs tile groups for ceil(pairs / tile_rows) + experts tiles");
   if (T <= 0) return 0;
-  VB_LAUNCH_PDL(moe_group_kernel, 1, 1024, 0, stream, d_row_off, d_sorted_token, d_pair_row, d_idx, T, experts, top);
+  VB_LAUNCH_PDL(moe_group_kernel, 1, 1024, 0, stream, d_row_off, d_sorted_token, d_pair_row, d_idx, T, experts, top,
+                tile_rows, d_tile_group, n_tiles);
+  return 0;
+}
+
+int vb_moe_gather_rows(void* d_out, const void* d_x, const int32_t* d_token, int rows, int width, void* stream) {
+  VB_CHECK_ARG(d_out && d_x && d_token && width % 8 == 0, "vb_moe_gather_rows: bad arguments (bf16 rows, width %% 8 == 0)");
+  if (rows <= 0) return 0;
+  VB_LAUNCH_PDL(moe_gather_rows_kernel, rows, 128, 0, stream, static_cast<uint4*>(d_out), static_cast<const uint4*>(d_x),
+                d_token, width / 8);
   return 0;
 }
 

@@ -225,10 +225,19 @@ class HybridWeights:
                     names = [f"e{e}" for e in range(f.experts)] + (["shared"] if f.shared_ff else [])
                     gate = torch.cat([mat(p + f"mlp.{n}.gate") for n in names], 0)
                     up = torch.cat([mat(p + f"mlp.{n}.up") for n in names], 0)
-                    half = ops.gate_up_tile_half(n_all)
+                    # a gate/up tile height that divides every expert keeps tiles from straddling experts: the stacked
+                    # buffer is then also the per-expert buffers one after the other, which the grouped form indexes
+                    fit = [hh for hh in (64, 48, 32, 16) if f.ff % hh == 0 and f.shared_ff % hh == 0]
+                    half = fit[0] if fit else ops.gate_up_tile_half(n_all)
                     w["gu_all"] = ops.pack_weight(ops.interleave_gate_up(gate, up, half), 2 * half)
                     del gate, up
                     w["down_all"] = ops.pack_weight(torch.cat([mat(p + f"mlp.{n}.down") for n in names], 1).contiguous(), 128)
+                    if fit and f.ff % 64 == 0:
+                        gb = ops.weight_tiles_bytes(2 * f.ff, cfg.width, 2 * half)
+                        w["grouped"] = {"group_bytes": gb, "kb_total": (n_all + 63) // 64, "group_kb": f.ff // 64}
+                        if f.shared_ff:
+                            w["s_gu_view"] = ops.PackedWeight(w["gu_all"].data[f.experts * gb:], 2 * f.shared_ff, cfg.width,
+                                                              2 * half)
                 else:
                     w["gu"] = torch.stack([mat(p + f"mlp.e{e}.gate", p + f"mlp.e{e}.up") for e in range(f.experts)]).contiguous()
                     w["down"] = torch.stack([mat(p + f"mlp.e{e}.down") for e in range(f.experts)]).contiguous()
@@ -255,7 +264,8 @@ class HybridWeights:
             elif isinstance(o, dict):
                 for x in o.values():
                     walk(x)
-        walk([self.embed, self.head, self.final_norm, self.layers])
+        walk([self.embed, self.head, self.final_norm,
+              [{k: v for k, v in L.items() if k != "s_gu_view"} for L in self.layers]])      # (views of other entries)
         return n
 
 
@@ -350,14 +360,19 @@ class HybridEngine:
                 self.cs[m.rotary.key()] = torch.zeros(R, 2, m.rotary.dims // 2, dtype=F32, device=dev)
         if moe:
             top, E = max(f.top for f in moe), max(f.experts for f in moe)
+            # grouped tensor-core form: row tiles of GROUP_TILE rows, every expert's rows padded to whole tiles
+            self.moe_tiles = (R * top + self.GROUP_TILE - 1) // self.GROUP_TILE + E
+            rmax = self.moe_tiles * self.GROUP_TILE
+            self.moe_tile_group = torch.zeros(self.moe_tiles, dtype=I32, device=dev)
+            self.moe_xs = torch.zeros(rmax * W if weights.tensor_core else 8, dtype=CT, device=dev)
             self.moe_idx = torch.zeros(R * top, dtype=I32, device=dev)
             self.moe_wts = torch.zeros(R * top, dtype=F32, device=dev)
             self.moe_row_off = torch.zeros(E + 1, dtype=I32, device=dev)
-            self.moe_sorted = torch.zeros(R * top, dtype=I32, device=dev)
+            self.moe_sorted = torch.zeros(rmax, dtype=I32, device=dev)
             self.moe_pair_row = torch.zeros(R * top, dtype=I32, device=dev)
-            self.moe_act = torch.zeros(R * max(max(f.top * f.ff, f.experts * f.ff + f.shared_ff) for f in moe), dtype=CT,
-                                       device=dev)
-            self.moe_out = torch.zeros(R * top * W, dtype=F32, device=dev)
+            self.moe_act = torch.zeros(max(R * max(max(f.top * f.ff, f.experts * f.ff + f.shared_ff) for f in moe),
+                                           rmax * max(f.ff for f in moe)), dtype=CT, device=dev)
+            self.moe_out = torch.zeros(rmax * W, dtype=F32, device=dev)
             self.s_act = torch.zeros(R * max([f.shared_ff for f in moe] + [1]), dtype=CT, device=dev)
             self.s_out = torch.zeros(R, W, dtype=F32, device=dev)
         self.sms = ops.device_info()[0] if dev.type == "cuda" else 1
@@ -367,6 +382,9 @@ class HybridEngine:
         self.first_vmix = next((i for i, L in enumerate(cfg.layers) if L.kind == "attention" and L.mixer.v_mix), None)
         self.layer_tap = None          # set to a list: the residual stream after every layer is appended (tests)
         self.use_tiled_attention = True
+
+    GROUP_TILE = 128          # rows per tile of the grouped expert projections
+    GROUPED_MIN_ROWS = 512    # steps with at least this many rows run the experts grouped; smaller ones in the dense form
 
     # ---- projections -----------------------------------------------------------------------------------------
     def _proj(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0, reduce: bool = True) -> torch.Tensor:
@@ -441,6 +459,28 @@ class HybridEngine:
         h = self.h[:T]
         idx, wts = self.moe_idx[:T * f.top], self.moe_wts[:T * f.top]
         ops.moe_route(h, w["router"], w["router_b"], f.top, idx, wts)
+        if "grouped" in w and T >= self.GROUPED_MIN_ROWS:
+            # compute-bound steps: tokens sorted by expert into whole row tiles, each tile multiplied by its expert's slice of
+            # the same packed buffers the dense form uses (tcgen05, gemm.cu), the shared expert as two plain projections
+            g, tt = w["grouped"], self.GROUP_TILE
+            n_tiles = (T * f.top + tt - 1) // tt + f.experts
+            rows = n_tiles * tt
+            ops.moe_group(idx, T, f.experts, f.top, self.moe_row_off, self.moe_sorted, self.moe_pair_row, tile_rows=tt,
+                          tile_group=self.moe_tile_group[:n_tiles])
+            xs = ops.moe_gather_rows(h, self.moe_sorted, self.moe_xs[:rows * W].view(rows, W))
+            act = self.moe_act[:rows * f.ff].view(rows, f.ff)
+            ops.gemm_grouped(xs, w["gu_all"], act, 2, 2 * f.ff, W, tt, self.moe_tile_group, group_bytes=g["group_bytes"],
+                             n_out=f.ff)
+            eo = self.moe_out[:rows * W].view(rows, W)
+            ops.gemm_grouped(act, w["down_all"], eo, 1, W, f.ff, tt, self.moe_tile_group, w_kb_stride=g["kb_total"],
+                             group_kb=g["group_kb"])
+            shared = None
+            if f.shared_ff:
+                sa = self.s_act[:T * f.shared_ff].view(T, f.shared_ff)
+                ops.gemm(h, w["s_gu_view"], mode=2, out=sa, tile_rows=w["s_gu_view"].tile_rows, n_out=f.shared_ff)
+                shared = ops.gemm_grouped(sa, w["down_all"], self.s_out[:T], 1, W, f.shared_ff, ops.gemm_t_tile(T), None,
+                                          w_kb_stride=g["kb_total"], kb_base=f.experts * g["group_kb"])
+            return ops.moe_combine(eo, shared, wts, self.moe_pair_row, f.top, self.y[:T])
         if "gu_all" in w:
             n_all = f.experts * f.ff + f.shared_ff
             act = self.moe_act[:T * n_all].view(T, n_all)

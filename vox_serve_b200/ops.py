@@ -1088,9 +1088,37 @@ def moe_route(h: torch.Tensor, router_w: torch.Tensor, router_b: Optional[torch.
 
 
 def moe_group(idx: torch.Tensor, T: int, experts: int, top: int, row_off: torch.Tensor, sorted_token: torch.Tensor,
-              pair_row: torch.Tensor) -> None:
+              pair_row: torch.Tensor, tile_rows: int = 0, tile_group: Optional[torch.Tensor] = None) -> None:
+    """Counting sort of the (token, choice) pairs by expert.  tile_rows > 0: the padded layout for grouped tensor-core
+    projections (every expert's rows start at a multiple of tile_rows, padding rows have token -1, tile_group[i] = expert of
+    row tile i); sorted_token must then hold tile_group.numel() * tile_rows entries."""
+    n_tiles = tile_group.numel() if tile_group is not None else 0
+    assert tile_rows == 0 or sorted_token.numel() >= n_tiles * tile_rows
     call("vb_moe_group", row_off.data_ptr(), sorted_token.data_ptr(), pair_row.data_ptr(), idx.data_ptr(), T, experts, top,
+         int(tile_rows), _p(tile_group), n_tiles, _stream())
+
+
+def moe_gather_rows(x: torch.Tensor, token: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[r] = x[token[r]] (zeros where token[r] < 0); bf16 rows."""
+    _need_cuda(x, token, out)
+    assert x.dtype == BF16 and out.dtype == BF16 and x.is_contiguous() and out.is_contiguous() and x.shape[1] == out.shape[1]
+    call("vb_moe_gather_rows", out.data_ptr(), x.data_ptr(), token.data_ptr(), out.shape[0], x.shape[1], _stream())
+    return out
+
+
+def gemm_grouped(x: torch.Tensor, w: "PackedWeight", out: torch.Tensor, mode: int, N: int, K: int, t_tile: int,
+                 tile_group: Optional[torch.Tensor], group_bytes: int = 0, w_kb_stride: int = 0, group_kb: int = 0,
+                 kb_base: int = 0, n_out: Optional[int] = None) -> torch.Tensor:
+    """Projection of row tiles (t_tile rows each) by the weights of their group inside one packed buffer (see vb_api.h):
+    N, K are one group's problem sizes.  mode 1 -> fp32 out [T, N]; mode 2 -> bf16 out [T, n_out] = silu(gate) * up."""
+    _need_cuda(x, out)
+    assert x.dtype == BF16 and x.dim() == 2 and x.shape[1] == K and out.is_contiguous()
+    assert tile_group is None or x.shape[0] % t_tile == 0
+    n_out = (N // 2 if mode == 2 else N) if n_out is None else n_out
+    call("vb_gemm_bf16_grouped", out.data_ptr(), w.data.data_ptr(), tensor_map_2d(x, t_tile).ptr, x.shape[0], N, K, n_out,
+         mode, w.tile_rows, n_out, t_tile, _p(tile_group), int(group_bytes), int(w_kb_stride), int(group_kb), int(kb_base),
          _stream())
+    return out
 
 
 def moe_combine(expert_out: torch.Tensor, shared_out: Optional[torch.Tensor], wts: torch.Tensor, pair_row: torch.Tensor,
