@@ -149,6 +149,22 @@ __global__ void moe_scale_dense_kernel(__nv_bfloat16* __restrict__ act, const in
   __syncthreads();
   __nv_bfloat16* row = act + t * ld;
   const int n = E * ff;
+  if ((ff & 7) == 0 && (ld & 7) == 0) {            // eight columns (16 bytes) of one expert at a time
+    uint4* row4 = reinterpret_cast<uint4*>(row);
+    for (int v = threadIdx.x; v < n / 8; v += blockDim.x) {
+      const float w = we[v * 8 / ff];
+      uint4 x = make_uint4(0u, 0u, 0u, 0u);
+      if (w != 0.f) {
+        x = row4[v];
+        x.x = pack_bf16(w * bf16_lo(x.x), w * bf16_hi(x.x));
+        x.y = pack_bf16(w * bf16_lo(x.y), w * bf16_hi(x.y));
+        x.z = pack_bf16(w * bf16_lo(x.z), w * bf16_hi(x.z));
+        x.w = pack_bf16(w * bf16_lo(x.w), w * bf16_hi(x.w));
+      }
+      row4[v] = x;
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < n; c += blockDim.x) {
     const float w = we[c / ff];
     row[c] = w == 0.f ? __float2bfloat16_rn(0.f) : __float2bfloat16_rn(w * __bfloat162float(row[c]));

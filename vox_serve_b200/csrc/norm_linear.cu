@@ -71,7 +71,6 @@ __global__ void layernorm_kernel(OT* __restrict__ out, const float* __restrict__
 }
 
 // x[t] += LN(y[t]; w1, b1);  optionally out2[t] = LN(x[t]; w2, b2) (the pre-norm of the sublayer that follows)
-// (if (out2 == nullptr) return sits between two barriers of block_sum calls: it is uniform over the block)
 template <typename OT>
 __global__ void postnorm_residual_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ w1,
                                          const float* __restrict__ b1, OT* __restrict__ out2,

@@ -16,8 +16,7 @@ There is no codec: ``run_detokenize`` hands each new token id to the client as 4
 """
 from __future__ import annotations
 
-import queue
-from typing import Coroutine, Dict, List, Optional
+from typing import Dict, List, Optional
 
 import numpy as np
 import torch
