@@ -188,9 +188,11 @@ int vb_set_gemm_smem_kb(int ring_kb, int gate_up_ring_kb);
 /* d_x_tiles (optional): X in the XT(vb_gemm_t_tile(T)) layout -- then x_map may be NULL; y_tiled (mode 2 only): write
  * Y in the XT(vb_gemm_t_tile(T)) layout over n_out columns (it is the down projection's activation). */
 int vb_gemm_bf16(void* d_y, const void* d_w_tiles, const void* x_map, const void* d_x_tiles, int T, int N, int K,
-                 int ldy, int mode, int split_k, int tile_rows, int n_out, int y_tiled, const void* d_bias, void* stream);
+                 int ldy, int mode, int split_k, int tile_rows, int n_out, int y_tiled, const void* d_bias, int act,
+                 void* stream);
 /* (d_bias: optional bf16 [N], mode 0 only: y = bf16(x w^T + bias), one rounding -- nn.Linear with bias, e.g.
- * Qwen3-TTS small_to_mtp_projection, vox_serve/model/qwen3_tts.py:923-930) */
+ * Qwen3-TTS small_to_mtp_projection, vox_serve/model/qwen3_tts.py:923-930.
+ * act, mode 0 only, applied to the fp32 value before the rounding: 0 none, 1 relu(y)^2, 2 gelu (erf), 3 gelu (tanh)) */
 
 /* ---- fused decode projections (T <= 64): one launch each for what orpheus.py:81-151 does between Linears ----
  * x_map: vb_tensor_map_2d_bf16(X, T, K, ldx, t_tile) with t_tile = 16 / 32 / 64 (smallest >= T).
@@ -468,15 +470,24 @@ int vb_codec_attn_chunk(float* d_out, const float* d_qkv, float* d_cache, int64_
 /* vb_gemm_bf16 with grouped weights (mixture of experts): the rows of token tile i (t_tile rows; x row-major through
  * x_map whose box is t_tile rows) multiply the weights of group d_tile_group[i] (NULL: group 0).  Group g's matrix lies
  * group_bytes * g further in d_w_tiles (matrices stacked along N) and / or its k-blocks lie group_kb * g + kb_base further
- * inside rows of w_kb_stride k-blocks (matrices stacked along K; 0 = ceil(K / 64)).  mode 1: fp32 [T][ldy]; mode 2:
- * silu(gate) * up, bf16 [T][ldy]. */
+ * inside rows of w_kb_stride k-blocks (matrices stacked along K; 0 = ceil(K / 64)).  mode 0: bf16 [T][ldy] after `act`
+ * (as vb_gemm_bf16); mode 1: fp32 [T][ldy]; mode 2: silu(gate) * up, bf16 [T][ldy]. */
 int vb_gemm_bf16_grouped(void* d_y, const void* d_w_tiles, const void* x_map, int T, int N, int K, int ldy, int mode,
                          int tile_rows, int n_out, int t_tile, const int32_t* d_tile_group, long long group_bytes,
-                         int w_kb_stride, int group_kb, int kb_base, void* stream);
+                         int w_kb_stride, int group_kb, int kb_base, int act, void* stream);
 
 /* ---- hybrid decoder stacks with an fp32 residual stream (norm_linear.cu, window_attn.cu, linear_attn.cu, moe.cu) ----
  * dtype arguments: 0 = bf16, 1 = fp32.  Norm weights, router weights, decays and recurrent states are always fp32.
- * vb_embed_rows_f32:        out[t] = table[ids[t]] widened to fp32
+ * vb_embed_rows_f32:        out[t] = table[ids[t]] widened to fp32 (+ pos_table[pos[t]] when a table of learned positions
+ *                           [n_pos][width] of the same type is given)
+ * vb_rmsnorm2_f32:          out1[t] = x[r] / sqrt(mean(x[r]^2) + eps) * w1, out2[t] the same with w2 (optional), r = rows ?
+ *                           rows[t] : t
+ * vb_residual_side_f32:     tail of a block with parallel sublayers: x[t] += mult * (y1[t] + y2[t]) (y2 optional); with a
+ *                           side input: g = gelu_tanh(Wg x[t]) * side_embed[ids[t]][e_off .. e_off + side_dim), y = Wp g,
+ *                           x[t] += mult * y / sqrt(mean(y^2) + eps) * side_norm; then out1 / out2 = RMS norms of x[t] with
+ *                           w1 / w2 (optional).  Wg [side_dim][width], Wp [width][side_dim], side_embed [vocab][ld_e] have
+ *                           type w_dtype; all arithmetic fp32
+ * vb_softcap_f32:           x[i] = cap * tanh(x[i] / cap) in place
  * vb_layernorm_f32:         out[t] = (x[r] - mean) / sqrt(var + eps) * w + b with r = rows ? rows[t] : t
  * vb_postnorm_residual_f32: x[t] += LN(y[t]; w1, b1); if out2: out2[t] = LN(x[t]; w2, b2).  y [y_planes][T][width]: the fp32
  *                           planes of a split-K projection are summed on the way in
@@ -484,7 +495,14 @@ int vb_gemm_bf16_grouped(void* d_y, const void* d_w_tiles, const void* x_map, in
  *                           group g owns rows row_off[g]..row_off[g+1] (T = upper bound of a group's rows), src(r) =
  *                           gather ? gather[r] : r.  epilogue 1: W = N gate rows then N up rows, Y = silu(gate) * up */
 int vb_embed_rows_f32(float* d_out, const void* d_table, const int32_t* d_ids, int T, int width, int vocab, int dtype,
-                      void* stream);
+                      const void* d_pos_table, const int32_t* d_pos, int n_pos, void* stream);
+int vb_rmsnorm2_f32(void* d_out1, void* d_out2, const float* d_x, const float* d_w1, const float* d_w2,
+                    const int32_t* d_rows, int T, int width, float eps, int out_dtype, void* stream);
+int vb_residual_side_f32(float* d_x, const float* d_y1, const float* d_y2, float mult, const void* d_side_gate,
+                         const void* d_side_proj, const float* d_side_norm, const void* d_side_embed, const int32_t* d_ids,
+                         int side_dim, int ld_e, int e_off, int vocab, int w_dtype, void* d_out1, const float* d_w1,
+                         void* d_out2, const float* d_w2, int T, int width, float eps, int out_dtype, void* stream);
+int vb_softcap_f32(float* d_x, long long n, float cap, void* stream);
 int vb_layernorm_f32(void* d_out, const float* d_x, const float* d_w, const float* d_b, const int32_t* d_rows, int T,
                      int width, float eps, int out_dtype, void* stream);
 int vb_postnorm_residual_f32(float* d_x, const float* d_y, int y_planes, const float* d_w1, const float* d_b1, void* d_out2,
@@ -493,6 +511,13 @@ int vb_postnorm_residual_f32(float* d_x, const float* d_y, int y_planes, const f
 int vb_linear(void* d_out, const void* d_x, const void* d_w, int T, int N, int K, int ldx, int ldo, int in_dtype,
               int out_dtype, int epilogue, float alpha, const int32_t* d_row_off, const int32_t* d_gather, int groups,
               long long w_group_stride, void* stream);
+/* (vb_linear epilogues 2, 3, 4: relu(y)^2, gelu (erf), gelu (tanh).)
+ * vb_linear_batched: `groups` independent products that share their rows (the heads of a token side by side): group g reads
+ * X + g * x_group_stride, W + g * w_group_stride and writes Y + g * o_group_stride, all with T rows; with d_gate,
+ * Y[r][n] *= sigmoid(d_gate[r * ld_gate + g]).  Epilogues 0, 2, 3, 4. */
+int vb_linear_batched(void* d_out, const void* d_x, const void* d_w, int T, int N, int K, int ldx, int ldo,
+                      long long x_group_stride, long long o_group_stride, long long w_group_stride, int groups, int in_dtype,
+                      int out_dtype, int epilogue, float alpha, const float* d_gate, int ld_gate, void* stream);
 int vb_cast_f32_bf16(void* d_out, const float* d_in, long long n, void* stream);
 /* out[i] = sum_s partials[s * n + i], s < planes, in plane order (fp32 partial planes of a split-K projection) */
 int vb_sum_planes_f32(float* d_out, const float* d_partials, int planes, long long n, void* stream);
@@ -513,6 +538,15 @@ int vb_qkv_rotary_append(const float* d_proj, int ldp, int q_off, int k_off, int
                          void* d_q_out, void* d_k_cache, void* d_v_cache, const int32_t* d_row_req, const int32_t* d_pos,
                          const int32_t* d_page_indptr, const int32_t* d_page_indices, int page_size, int T, int H, int G,
                          int dim, int vdim, int vmix, float* d_v_first, const float* d_lambda, int dtype, void* stream);
+/* Latent attention, the tail of the fused (query latent | key/value latent | ...) projection rows [T][ldp] (fp32): both
+ * latents are RMS-normed (weights d_wq [q_rank], d_wc [kv_rank]); the query latent goes to d_cq_out [T][q_rank], the
+ * key/value latent to position pos[t] of request row_req[t] in d_c_cache [pages][page][kv_rank] (NULL: a layer that reads
+ * another layer's latents).  Attention over the latents runs through vb_window_attn with ONE key/value head of kv_rank dims
+ * that is both key and value (queries carried into latent space by vb_linear_batched). */
+int vb_latent_norm_append(const float* d_proj, int ldp, int q_off, int c_off, int q_rank, int kv_rank, const float* d_wq,
+                          const float* d_wc, void* d_cq_out, void* d_c_cache, const int32_t* d_row_req, const int32_t* d_pos,
+                          const int32_t* d_page_indptr, const int32_t* d_page_indices, int page_size, int T, float eps,
+                          int dtype, void* stream);
 int vb_window_attn(void* d_out, const void* d_q, const void* d_k_cache, const void* d_v_cache, const float* d_gate,
                    int ld_gate, const int32_t* d_row_req, const int32_t* d_pos, const int32_t* d_page_indptr,
                    const int32_t* d_page_indices, int T, int H, int G, int dim, int vdim, int page_size, int window,
@@ -543,6 +577,12 @@ int vb_gated_rmsnorm(void* d_out, const float* d_x, const float* d_w, const floa
 /* Mixture of experts: routing, grouping by expert, weighted combination (the experts run through vb_linear) */
 int vb_moe_route(int32_t* d_idx, float* d_wts, const void* d_h, const float* d_router_w, const float* d_router_b, int T,
                  int width, int experts, int top, int h_dtype, void* stream);
+/* scores s = sigmoid(W_r h); chosen: the `top` largest s + correction among the experts of the `keep` best of n_groups
+ * groups of neighbours (group score: its two largest corrected scores summed; n_groups <= 1: all experts); weights: the
+ * chosen s / (their sum + 1e-20).  d_shared_gate_w [width] (optional): d_shared_gate[t] = sigmoid(w . h[t]) */
+int vb_moe_route_sigmoid(int32_t* d_idx, float* d_wts, float* d_shared_gate, const void* d_h, const float* d_router_w,
+                         const float* d_correction, const float* d_shared_gate_w, int T, int width, int experts, int top,
+                         int n_groups, int keep, int h_dtype, void* stream);
 int vb_moe_group(int32_t* d_row_off, int32_t* d_sorted_token, int32_t* d_pair_row, const int32_t* d_idx, int T,
                  int experts, int top, int tile_rows, int32_t* d_tile_group, int n_tiles, void* stream);
 /* (tile_rows > 0: every expert's rows start at a multiple of tile_rows; padding rows get token -1; d_tile_group[i] =
@@ -552,9 +592,11 @@ int vb_moe_gather_rows(void* d_out, const void* d_x, const int32_t* d_token, int
 /* dense form (bf16): act [T][ld] holds silu(gate) * up of EVERY expert side by side (expert e at columns e * ff ..), then
  * the shared expert's; columns of expert e are scaled by the token's routing weight for e, or zeroed if e was not chosen */
 int vb_moe_scale_dense(void* d_act, const int32_t* d_idx, const float* d_wts, int T, int ld, int experts, int ff, int top,
-                       void* stream);
+                       const float* d_shared_gate, int shared_ff, void* stream);
+/* (d_shared_gate [T], optional: the shared expert's shared_ff columns, which follow the experts', times the token's gate) */
 int vb_moe_combine(float* d_y, const float* d_expert_out, const float* d_shared_out, const float* d_wts,
-                   const int32_t* d_pair_row, int T, int width, int top, void* stream);
+                   const int32_t* d_pair_row, int T, int width, int top, const float* d_shared_scale, void* stream);
+/* (d_shared_scale [T], optional: the shared expert's output enters times that per-token factor) */
 
 #ifdef __cplusplus
 }

@@ -52,7 +52,7 @@ SIGNATURES = {
     "vb_set_gemm_smem_kb": (c_int, [c_int, c_int]),
     "vb_weight_tiles_bytes": (c_size_t, [c_int, c_int, c_int]),
     "vb_pack_weight_tiles": (c_int, [P, P, c_int, c_int, c_int64, c_int, P]),
-    "vb_gemm_bf16": (c_int, [P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P]),
+    "vb_gemm_bf16": (c_int, [P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, c_int, P]),
     "vb_proj_residual": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P]),
     "vb_proj_norm_gateup_silu": (c_int, [P, P, P, P, P, c_int, P, c_float, c_int, c_int, c_int, c_int, c_int, c_int, P]),
     "vb_proj_norm_qkv_rope_append": (c_int, [P, P, P, P, P, P, c_int, P, c_float, P, P, P, c_int, c_int, c_int, c_int,
@@ -103,7 +103,16 @@ SIGNATURES = {
     "vb_codec_rmsnorm": (c_int, [P, P, P, c_int, c_int, c_int, c_float, P]),
     "vb_codec_attn_chunk": (c_int, [P, P, P, c_int64, P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, P]),
     "vb_orpheus_window_codes": (c_int, [P, P, P, P, c_int, c_int, P]),
-    "vb_embed_rows_f32": (c_int, [P, P, P, c_int, c_int, c_int, c_int, P]),
+    "vb_embed_rows_f32": (c_int, [P, P, P, c_int, c_int, c_int, c_int, P, P, c_int, P]),
+    "vb_rmsnorm2_f32": (c_int, [P, P, P, P, P, P, c_int, c_int, c_float, c_int, P]),
+    "vb_residual_side_f32": (c_int, [P, P, P, c_float, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P, P, P, c_int,
+                                     c_int, c_float, c_int, P]),
+    "vb_softcap_f32": (c_int, [P, C.c_longlong, c_float, P]),
+    "vb_linear_batched": (c_int, [P, P, P, c_int, c_int, c_int, c_int, c_int, C.c_longlong, C.c_longlong, C.c_longlong, c_int,
+                                  c_int, c_int, c_int, c_float, P, c_int, P]),
+    "vb_latent_norm_append": (c_int, [P, c_int, c_int, c_int, c_int, c_int, P, P, P, P, P, P, P, P, c_int, c_int, c_float,
+                                      c_int, P]),
+    "vb_moe_route_sigmoid": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P]),
     "vb_layernorm_f32": (c_int, [P, P, P, P, P, c_int, c_int, c_float, c_int, P]),
     "vb_postnorm_residual_f32": (c_int, [P, P, c_int, P, P, P, P, P, c_int, c_int, c_float, c_int, P]),
     "vb_linear": (c_int, [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, P, P, c_int,
@@ -128,9 +137,9 @@ SIGNATURES = {
     "vb_moe_group": (c_int, [P, P, P, P, c_int, c_int, c_int, c_int, P, c_int, P]),
     "vb_moe_gather_rows": (c_int, [P, P, P, c_int, c_int, P]),
     "vb_gemm_bf16_grouped": (c_int, [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, C.c_longlong,
-                                     c_int, c_int, c_int, P]),
-    "vb_moe_combine": (c_int, [P, P, P, P, P, c_int, c_int, c_int, P]),
-    "vb_moe_scale_dense": (c_int, [P, P, P, c_int, c_int, c_int, c_int, c_int, P]),
+                                     c_int, c_int, c_int, c_int, P]),
+    "vb_moe_combine": (c_int, [P, P, P, P, P, c_int, c_int, c_int, P, P]),
+    "vb_moe_scale_dense": (c_int, [P, P, P, c_int, c_int, c_int, c_int, c_int, P, c_int, P]),
 }
 
 _lock = threading.Lock()

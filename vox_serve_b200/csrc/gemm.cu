@@ -61,8 +61,10 @@ struct GemmParams {
   const int32_t* row_page;
   const int32_t* row_slot;
   int n_q, n_kv, page_size;
-  // mode 0: optional bias [N] added in fp32 before the single bf16 rounding (nn.Linear with bias)
+  // mode 0: optional bias [N] added in fp32 before the single bf16 rounding (nn.Linear with bias), then an optional
+  // activation (GemmAct) on the fp32 value
   const __nv_bfloat16* bias;
+  int act;
   // grouped weights (mixture of experts): token tile t_blk multiplies the weights of group tile_group[t_blk] (nullptr:
   // group 0).  A group's matrix starts group_bytes after the previous one (matrices stacked along N), and / or its k-blocks
   // start group_kb after the previous one's inside rows of w_kb_stride k-blocks (matrices stacked along K; 0: the
@@ -71,6 +73,14 @@ struct GemmParams {
   long long group_bytes;
   int w_kb_stride, group_kb, kb_base;
 };
+
+enum GemmAct { GA_NONE = 0, GA_RELU_SQ = 1, GA_GELU_ERF = 2, GA_GELU_TANH = 3 };
+__device__ __forceinline__ float gemm_act(float v, int act) {
+  if (act == GA_RELU_SQ) { const float r = fmaxf(v, 0.f); return r * r; }
+  if (act == GA_GELU_ERF) return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+  if (act == GA_GELU_TANH) return 0.5f * v * (1.f + tanhf(0.79788456080286536f * (v + 0.044715f * v * v * v)));
+  return v;
+}
 
 __device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 __device__ __forceinline__ uint32_t dsmem_addr(const void* local_ptr, uint32_t cta_rank) {
@@ -377,7 +387,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2) gemm_bf16_kernel(const GemmPa
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int t = t_base + c0 + j;
-              if (t < p.T) y[static_cast<size_t>(t) * p.ldy + n] = __float2bfloat16_rn(__uint_as_float(v[j]) + bv);
+              if (t < p.T) y[static_cast<size_t>(t) * p.ldy + n] = __float2bfloat16_rn(gemm_act(__uint_as_float(v[j]) + bv, p.act));
             }
           } else {
             float* y = static_cast<float*>(p.y) + static_cast<size_t>(split) * p.T * p.ldy;
@@ -699,8 +709,10 @@ int vb_gemm_t_tile(int T) {
 }
 
 int vb_gemm_bf16(void* d_y, const void* d_w_tiles, const void* x_map, const void* d_x_tiles, int T, int N, int K,
-                 int ldy, int mode, int split_k, int tile_rows, int n_out, int y_tiled, const void* d_bias, void* stream) {
+                 int ldy, int mode, int split_k, int tile_rows, int n_out, int y_tiled, const void* d_bias, int act,
+                 void* stream) {
   VB_CHECK_ARG(d_y && d_w_tiles && (x_map || d_x_tiles), "vb_gemm_bf16: null pointer");
+  VB_CHECK_ARG(act >= 0 && act <= 3 && (act == 0 || mode == 0), "vb_gemm_bf16: activation %d is a mode 0 option", act);
   VB_CHECK_ARG(!d_bias || mode == 0, "vb_gemm_bf16: bias is a mode 0 option");
   VB_CHECK_ARG(!y_tiled || mode == 2, "vb_gemm_bf16: tiled output is a mode 2 option");
   VB_CHECK_ARG(mode >= 0 && mode <= 2, "vb_gemm_bf16: mode %d", mode);
@@ -714,14 +726,16 @@ int vb_gemm_bf16(void* d_y, const void* d_w_tiles, const void* x_map, const void
   p.t_tile = vb_gemm_t_tile(T);
   p.y_tiled = y_tiled;
   p.bias = static_cast<const __nv_bfloat16*>(d_bias);
+  p.act = act;
   return launch_gemm(p, d_w_tiles, x_map, static_cast<cudaStream_t>(stream), d_x_tiles);
 }
 
 int vb_gemm_bf16_grouped(void* d_y, const void* d_w_tiles, const void* x_map, int T, int N, int K, int ldy, int mode,
                          int tile_rows, int n_out, int t_tile, const int32_t* d_tile_group, long long group_bytes,
-                         int w_kb_stride, int group_kb, int kb_base, void* stream) {
+                         int w_kb_stride, int group_kb, int kb_base, int act, void* stream) {
   VB_CHECK_ARG(d_y && d_w_tiles && x_map, "vb_gemm_bf16_grouped: null pointer");
-  VB_CHECK_ARG(mode == 1 || mode == 2, "vb_gemm_bf16_grouped: mode %d (1: fp32 out, 2: silu(gate) * up)", mode);
+  VB_CHECK_ARG(mode >= 0 && mode <= 2, "vb_gemm_bf16_grouped: mode %d (0: bf16 out, 1: fp32 out, 2: silu(gate) * up)", mode);
+  VB_CHECK_ARG(act >= 0 && act <= 3 && (act == 0 || mode == 0), "vb_gemm_bf16_grouped: activation %d is a mode 0 option", act);
   VB_CHECK_ARG(mode != 2 || (tile_rows % 32 == 0 && N % tile_rows == 0), "vb_gemm_bf16_grouped: mode 2 tile_rows");
   VB_CHECK_ARG(t_tile >= 16 && t_tile <= 256 && t_tile % 16 == 0, "vb_gemm_bf16_grouped: t_tile %d", t_tile);
   VB_CHECK_ARG(group_bytes >= 0 && w_kb_stride >= 0 && group_kb >= 0 && kb_base >= 0, "vb_gemm_bf16_grouped: offsets");
@@ -730,6 +744,7 @@ int vb_gemm_bf16_grouped(void* d_y, const void* d_w_tiles, const void* x_map, in
   p.tile_rows = tile_rows > 0 ? tile_rows : 128;
   p.n_out = n_out > 0 ? n_out : (mode == 2 ? N / 2 : N);
   p.t_tile = t_tile;
+  p.act = act;
   p.tile_group = d_tile_group; p.group_bytes = group_bytes; p.w_kb_stride = w_kb_stride; p.group_kb = group_kb; p.kb_base = kb_base;
   return launch_gemm(p, d_w_tiles, x_map, static_cast<cudaStream_t>(stream), nullptr);
 }
@@ -751,7 +766,7 @@ int vb_norm_lmhead(void* d_logits, const void* d_hidden, const void* d_norm_weig
   if (T <= 0) return 0;
   const int rc = vb_rmsnorm(d_workspace, d_hidden, d_norm_weight, T, K, eps, vb_gemm_t_tile(T), stream);
   if (rc != 0) return rc;
-  return vb_gemm_bf16(d_logits, d_w_tiles, nullptr, d_workspace, T, N, K, ldy, 0, 1, tile_rows, 0, 0, d_bias, stream);
+  return vb_gemm_bf16(d_logits, d_w_tiles, nullptr, d_workspace, T, N, K, ldy, 0, 1, tile_rows, 0, 0, d_bias, 0, stream);
 }
 
 int vb_proj_residual(void* d_hidden_out, void* d_hidden_tiles_out, float* d_ssq_out, const void* d_w_tiles,

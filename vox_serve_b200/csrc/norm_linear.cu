@@ -33,15 +33,145 @@ __device__ __forceinline__ float block_sum(float v, float* red, int& phase) {
   return warp_sum(t);
 }
 
+// out[t] = table[ids[t]] (+ pos_table[pos[t]]: learned absolute positions, added unscaled in fp32)
 template <typename WT>
 __global__ void embed_rows_kernel(float* __restrict__ out, const WT* __restrict__ table, const int32_t* __restrict__ ids,
-                                  int W, int vocab) {
+                                  int W, int vocab, const WT* __restrict__ pos_table, const int32_t* __restrict__ pos,
+                                  int n_pos) {
   pdl_sync();
   const int t = blockIdx.x;
   int id = ids[t];
   id = min(max(id, 0), vocab - 1);
   const WT* src = table + static_cast<size_t>(id) * W;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) out[static_cast<size_t>(t) * W + i] = to_f(src[i]);
+  const WT* ps = nullptr;
+  if (pos_table) ps = pos_table + static_cast<size_t>(min(max(pos[t], 0), n_pos - 1)) * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x)
+    out[static_cast<size_t>(t) * W + i] = to_f(src[i]) + (ps ? to_f(ps[i]) : 0.f);
+}
+
+// RMS norm of a row with one or two weights: out1[t] = x[r] / sqrt(mean(x[r]^2) + eps) * w1, out2[t] likewise with w2
+// (the two sublayers of a parallel block read differently weighted norms of the same row)
+template <typename OT>
+__global__ void rmsnorm2_kernel(OT* __restrict__ out1, OT* __restrict__ out2, const float* __restrict__ x,
+                                const float* __restrict__ w1, const float* __restrict__ w2, int W, float eps,
+                                const int32_t* __restrict__ rows) {
+  extern __shared__ float sm[];
+  float* row = sm;
+  float* red = sm + W;
+  int phase = 0;
+  pdl_sync();
+  const size_t t = blockIdx.x;
+  const size_t src = rows ? static_cast<size_t>(rows[t]) : t;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = x[src * W + i];
+    row[i] = v;
+    q = fmaf(v, v, q);
+  }
+  const float rs = 1.f / sqrtf(block_sum(q, red, phase) / W + eps);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = row[i] * rs;
+    out1[t * W + i] = from_f<OT>(v * w1[i]);
+    if (out2) out2[t * W + i] = from_f<OT>(v * w2[i]);
+  }
+}
+
+__device__ __forceinline__ float act_apply(float v, int act) {
+  // 2: relu(v)^2   3: gelu, exact (erf)   4: gelu, tanh form
+  if (act == 2) { const float r = fmaxf(v, 0.f); return r * r; }
+  if (act == 3) return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+  if (act == 4) return 0.5f * v * (1.f + tanhf(0.79788456080286536f * (v + 0.044715f * v * v * v)));
+  return v;
+}
+
+// The tail of a block whose sublayers run in parallel on the same residual row:
+//   x[t] += mult * (y1[t] + y2[t])
+//   per-token side input (optional): g = gelu_tanh(Wg x[t]) * e[t], y = Wp g, x[t] += mult * y / sqrt(mean(y^2) + eps) * ws
+//     with e[t] = side_embed[ids[t]][e_off .. e_off + side_dim)
+//   out1[t] = rms_norm(x[t]) * w1, out2[t] = rms_norm(x[t]) * w2 (optional: what the next block's sublayers read)
+// Everything in fp32 on the fp32 row; the side matrices are read in their storage type.
+struct ResidualSideParams {
+  float* x;
+  const float* y1;
+  const float* y2;
+  const void* side_gate;    // [side_dim][W]
+  const void* side_proj;    // [W][side_dim]
+  const float* side_norm;   // [W]
+  const void* side_embed;   // [vocab][ld_e]
+  const int32_t* ids;
+  void* out1;
+  void* out2;
+  const float* w1;
+  const float* w2;
+  int W, side_dim, ld_e, e_off, vocab;
+  float mult, eps;
+};
+
+template <typename WT, typename OT>
+__global__ void __launch_bounds__(256) residual_side_kernel(ResidualSideParams p) {
+  extern __shared__ float sm[];
+  const int W = p.W, SD = p.side_dim;
+  float* row = sm;              // [W]
+  float* yb = sm + W;           // [W]
+  float* g = yb + W;            // [SD]
+  float* red = g + SD;          // [64]
+  int phase = 0;
+  pdl_sync();
+  const size_t t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float y = p.y1[t * W + i];
+    if (p.y2) y += p.y2[t * W + i];
+    row[i] = fmaf(p.mult, y, p.x[t * W + i]);
+  }
+  __syncthreads();
+  if (p.side_gate) {
+    const WT* Wg = static_cast<const WT*>(p.side_gate);
+    const WT* Wp = static_cast<const WT*>(p.side_proj);
+    const int id = min(max(p.ids[t], 0), p.vocab - 1);
+    const WT* e = static_cast<const WT*>(p.side_embed) + static_cast<size_t>(id) * p.ld_e + p.e_off;
+    for (int d = warp; d < SD; d += nw) {
+      const WT* wr = Wg + static_cast<size_t>(d) * W;
+      float s = 0.f;
+      for (int i = lane; i < W; i += 32) s = fmaf(to_f(wr[i]), row[i], s);
+      s = warp_sum(s);
+      if (lane == 0) g[d] = act_apply(s, 4) * to_f(e[d]);
+    }
+    __syncthreads();
+    float q = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      const WT* wr = Wp + static_cast<size_t>(i) * SD;
+      float s = 0.f;
+      for (int d = 0; d < SD; ++d) s = fmaf(to_f(wr[d]), g[d], s);
+      yb[i] = s;
+      q = fmaf(s, s, q);
+    }
+    const float rs = 1.f / sqrtf(block_sum(q, red, phase) / W + p.eps);
+    for (int i = threadIdx.x; i < W; i += blockDim.x) row[i] = fmaf(p.mult, yb[i] * rs * p.side_norm[i], row[i]);
+    __syncthreads();
+  }
+  float q = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = row[i];
+    p.x[t * W + i] = v;
+    q = fmaf(v, v, q);
+  }
+  if (p.out1 == nullptr) return;
+  const float rs = 1.f / sqrtf(block_sum(q, red, phase) / W + p.eps);
+  OT* o1 = static_cast<OT*>(p.out1);
+  OT* o2 = static_cast<OT*>(p.out2);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = row[i] * rs;
+    o1[t * W + i] = from_f<OT>(v * p.w1[i]);
+    if (o2) o2[t * W + i] = from_f<OT>(v * p.w2[i]);
+  }
+}
+
+// logits <- cap * tanh(logits / cap)
+__global__ void softcap_kernel(float* __restrict__ x, long long n, float cap) {
+  pdl_sync();
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) x[i] = cap * tanhf(x[i] / cap);
 }
 
 // LayerNorm of a row: (x - mean) / sqrt(mean((x - mean)^2) + eps) * w + b, statistics in two passes over the row
@@ -122,7 +252,10 @@ __global__ void postnorm_residual_kernel(float* __restrict__ x, const float* __r
 // Y[r][n] = alpha * sum_k X[src(r)][k] * W[g][n][k]
 //   dense:   g = 0, r in [0, T), src(r) = r
 //   grouped: blockIdx.z = g, r in [row_off[g], row_off[g + 1]), src(r) = gather ? gather[r] : r
-// epilogue 0: store (OT);  1: W holds N "gate" rows followed by N "up" rows, store silu(gate) * up (OT)
+//   batched: blockIdx.z = g, every group has the rows [0, T): X, Y advance by x_group_stride, o_group_stride elements per
+//            group (heads of one row side by side), gate: Y[r][n] *= sigmoid(gate[r * ld_gate + g])
+// epilogue 0: store (OT);  1: W holds N "gate" rows followed by N "up" rows, store silu(gate) * up (OT);
+//          2: relu(y)^2;  3: gelu(y), exact;  4: gelu(y), tanh form
 // Tile 64 x 64, BK 16, 256 threads, 4 x 4 outputs per thread.
 // ------------------------------------------------------------------------------------------------------------------
 constexpr int LB_M = 64, LB_N = 64, LB_K = 16;
@@ -136,6 +269,9 @@ struct LinearParams {
   int T, N, K, ldx, ldo, epi;
   long long w_group_stride;     // elements between the weight matrices of consecutive groups
   float alpha;
+  long long x_group_stride, o_group_stride;     // batched form (both 0 otherwise)
+  const float* gate;
+  int ld_gate, batched;
 };
 
 template <typename XT, typename WT, typename OT, int EPI>
@@ -151,7 +287,7 @@ __global__ void __launch_bounds__(256) linear_kernel(LinearParams p) {
   }
   const int m0 = r_lo + blockIdx.x * LB_M, n0 = blockIdx.y * LB_N;
   if (m0 >= r_hi) return;
-  const XT* X = static_cast<const XT*>(p.x);
+  const XT* X = static_cast<const XT*>(p.x) + static_cast<size_t>(blockIdx.z) * p.x_group_stride;
   const WT* Wm = static_cast<const WT*>(p.w) + static_cast<size_t>(blockIdx.z) * p.w_group_stride;
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   // loader: row lr of the tile, 4 consecutive k starting at lk
@@ -195,11 +331,13 @@ __global__ void __launch_bounds__(256) linear_kernel(LinearParams p) {
     }
     __syncthreads();
   }
-  OT* out = static_cast<OT*>(p.out);
+  OT* out = static_cast<OT*>(p.out) + static_cast<size_t>(blockIdx.z) * p.o_group_stride;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int r = m0 + ty * 4 + i;
     if (r >= r_hi) continue;
+    float gmul = 1.f;
+    if (p.gate) gmul = 1.f / (1.f + expf(-p.gate[static_cast<size_t>(r) * p.ld_gate + blockIdx.z]));
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tx * 4 + j;
@@ -209,7 +347,7 @@ __global__ void __launch_bounds__(256) linear_kernel(LinearParams p) {
         const float g = acc[0][i][j], u = acc[NB - 1][i][j];
         v = g / (1.f + expf(-g)) * u;
       } else {
-        v = acc[0][i][j] * p.alpha;
+        v = act_apply(acc[0][i][j] * p.alpha, p.epi) * gmul;
       }
       out[static_cast<size_t>(r) * p.ldo + n] = from_f<OT>(v);
     }
@@ -259,12 +397,81 @@ using bf16 = __nv_bfloat16;
 extern "C" {
 
 int vb_embed_rows_f32(float* d_out, const void* d_table, const int32_t* d_ids, int T, int width, int vocab, int dtype,
-                      void* stream) {
+                      const void* d_pos_table, const int32_t* d_pos, int n_pos, void* stream) {
   VB_CHECK_ARG(d_out && d_table && d_ids && width > 0 && vocab > 0, "vb_embed_rows_f32: bad arguments");
+  VB_CHECK_ARG(!d_pos_table || (d_pos && n_pos > 0), "vb_embed_rows_f32: a position table needs positions");
   if (T <= 0) return 0;
-  if (dtype == 1) VB_LAUNCH_PDL(embed_rows_kernel<float>, T, 128, 0, stream, d_out, static_cast<const float*>(d_table), d_ids, width, vocab);
-  else VB_LAUNCH_PDL(embed_rows_kernel<bf16>, T, 128, 0, stream, d_out, static_cast<const bf16*>(d_table), d_ids, width, vocab);
+  if (dtype == 1) VB_LAUNCH_PDL(embed_rows_kernel<float>, T, 128, 0, stream, d_out, static_cast<const float*>(d_table), d_ids, width, vocab, static_cast<const float*>(d_pos_table), d_pos, n_pos);
+  else VB_LAUNCH_PDL(embed_rows_kernel<bf16>, T, 128, 0, stream, d_out, static_cast<const bf16*>(d_table), d_ids, width, vocab, static_cast<const bf16*>(d_pos_table), d_pos, n_pos);
   return 0;
+}
+
+int vb_rmsnorm2_f32(void* d_out1, void* d_out2, const float* d_x, const float* d_w1, const float* d_w2,
+                    const int32_t* d_rows, int T, int width, float eps, int out_dtype, void* stream) {
+  VB_CHECK_ARG(d_out1 && d_x && d_w1 && width > 0 && (!d_out2 || d_w2), "vb_rmsnorm2_f32: bad arguments");
+  if (T <= 0) return 0;
+  const size_t smem = (static_cast<size_t>(width) + 64) * sizeof(float);
+  VB_CHECK_ARG(smem <= static_cast<size_t>(VB_MAX_DYN_SMEM), "vb_rmsnorm2_f32: width %d too large", width);
+  if (out_dtype == 1) {
+    if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(rmsnorm2_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+    VB_LAUNCH_PDL(rmsnorm2_kernel<float>, T, 256, smem, stream, static_cast<float*>(d_out1), static_cast<float*>(d_out2), d_x, d_w1, d_w2, width, eps, d_rows);
+  } else {
+    if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(rmsnorm2_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+    VB_LAUNCH_PDL(rmsnorm2_kernel<bf16>, T, 256, smem, stream, static_cast<bf16*>(d_out1), static_cast<bf16*>(d_out2), d_x, d_w1, d_w2, width, eps, d_rows);
+  }
+  return 0;
+}
+
+}  // extern "C"
+
+template <typename WT, typename OT>
+static int launch_residual_side(const ResidualSideParams& p, int T, size_t smem, cudaStream_t stream) {
+  if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(residual_side_kernel<WT, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+  VB_LAUNCH_PDL((residual_side_kernel<WT, OT>), T, 256, smem, stream, p);
+  return 0;
+}
+
+extern "C" {
+
+int vb_residual_side_f32(float* d_x, const float* d_y1, const float* d_y2, float mult, const void* d_side_gate,
+                         const void* d_side_proj, const float* d_side_norm, const void* d_side_embed, const int32_t* d_ids,
+                         int side_dim, int ld_e, int e_off, int vocab, int w_dtype, void* d_out1, const float* d_w1,
+                         void* d_out2, const float* d_w2, int T, int width, float eps, int out_dtype, void* stream) {
+  VB_CHECK_ARG(d_x && d_y1 && width > 0, "vb_residual_side_f32: bad arguments");
+  VB_CHECK_ARG(!d_side_gate || (d_side_proj && d_side_norm && d_side_embed && d_ids && side_dim > 0 && vocab > 0 &&
+                                e_off >= 0 && e_off + side_dim <= ld_e),
+               "vb_residual_side_f32: the side input needs its matrices, norm weight, table and token ids");
+  VB_CHECK_ARG((!d_out1 || d_w1) && (!d_out2 || (d_out1 && d_w2)), "vb_residual_side_f32: norms need weights");
+  if (T <= 0) return 0;
+  const int sd = d_side_gate ? side_dim : 0;
+  const size_t smem = (2 * static_cast<size_t>(width) + sd + 64) * sizeof(float);
+  VB_CHECK_ARG(smem <= static_cast<size_t>(VB_MAX_DYN_SMEM), "vb_residual_side_f32: width %d too large", width);
+  ResidualSideParams p{d_x, d_y1, d_y2, d_side_gate, d_side_proj, d_side_norm, d_side_embed, d_ids, d_out1, d_out2, d_w1, d_w2,
+                       width, sd, ld_e, e_off, vocab, mult, eps};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (w_dtype == 1) return out_dtype == 1 ? launch_residual_side<float, float>(p, T, smem, s) : launch_residual_side<float, bf16>(p, T, smem, s);
+  return out_dtype == 1 ? launch_residual_side<bf16, float>(p, T, smem, s) : launch_residual_side<bf16, bf16>(p, T, smem, s);
+}
+
+int vb_softcap_f32(float* d_x, long long n, float cap, void* stream) {
+  VB_CHECK_ARG(d_x && cap > 0.f, "vb_softcap_f32: bad arguments");
+  if (n <= 0) return 0;
+  VB_LAUNCH_PDL(softcap_kernel, static_cast<unsigned>((n + 255) / 256), 256, 0, stream, d_x, n, cap);
+  return 0;
+}
+
+int vb_linear_batched(void* d_out, const void* d_x, const void* d_w, int T, int N, int K, int ldx, int ldo,
+                      long long x_group_stride, long long o_group_stride, long long w_group_stride, int groups, int in_dtype,
+                      int out_dtype, int epilogue, float alpha, const float* d_gate, int ld_gate, void* stream) {
+  VB_CHECK_ARG(d_out && d_x && d_w && N > 0 && K > 0 && groups >= 1, "vb_linear_batched: bad arguments");
+  VB_CHECK_ARG(epilogue == 0 || (epilogue >= 2 && epilogue <= 4), "vb_linear_batched: epilogue %d", epilogue);
+  VB_CHECK_ARG(!d_gate || ld_gate >= groups, "vb_linear_batched: gate rows hold one value per group");
+  if (T <= 0) return 0;
+  LinearParams p{d_out, d_x, d_w, nullptr, nullptr, T, N, K, ldx, ldo, epilogue, w_group_stride, alpha, x_group_stride,
+                 o_group_stride, d_gate, ld_gate, 1};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (in_dtype == 1) return out_dtype == 1 ? launch_linear<float, float, float>(p, groups, T, s) : launch_linear<float, float, bf16>(p, groups, T, s);
+  return out_dtype == 1 ? launch_linear<bf16, bf16, float>(p, groups, T, s) : launch_linear<bf16, bf16, bf16>(p, groups, T, s);
 }
 
 int vb_layernorm_f32(void* d_out, const float* d_x, const float* d_w, const float* d_b, const int32_t* d_rows, int T,
@@ -307,10 +514,10 @@ int vb_linear(void* d_out, const void* d_x, const void* d_w, int T, int N, int K
               int out_dtype, int epilogue, float alpha, const int32_t* d_row_off, const int32_t* d_gather, int groups,
               long long w_group_stride, void* stream) {
   VB_CHECK_ARG(d_out && d_x && d_w && N > 0 && K > 0 && ldx >= K && ldo >= N, "vb_linear: bad arguments");
-  VB_CHECK_ARG(epilogue == 0 || epilogue == 1, "vb_linear: epilogue %d", epilogue);
+  VB_CHECK_ARG(epilogue >= 0 && epilogue <= 4, "vb_linear: epilogue %d", epilogue);
   VB_CHECK_ARG(groups >= 1 && (groups == 1 || d_row_off), "vb_linear: grouped launches need row offsets");
   if (T <= 0) return 0;
-  LinearParams p{d_out, d_x, d_w, d_row_off, d_gather, T, N, K, ldx, ldo, epilogue, w_group_stride, alpha};
+  LinearParams p{d_out, d_x, d_w, d_row_off, d_gather, T, N, K, ldx, ldo, epilogue, w_group_stride, alpha, 0, 0, nullptr, 0, 0};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // in_dtype: 0 = bf16 activations and weights, 1 = fp32 both; out_dtype likewise
   if (in_dtype == 1) return out_dtype == 1 ? launch_linear<float, float, float>(p, groups, T, s) : launch_linear<float, float, bf16>(p, groups, T, s);

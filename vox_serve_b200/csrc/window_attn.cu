@@ -99,6 +99,54 @@ __global__ void qkv_rotary_append_kernel(QkvTailParams p) {
   }
 }
 
+// The tail of a fused (query latent | key/value latent | ...) projection of latent attention: both latents are RMS-normed
+// with their own weights in fp32; the query latent is written out for its up-projection, the key/value latent is appended
+// to the layer's pages as ONE head of kv_rank dims per token (the only thing such a layer caches: keys and values are
+// per-head expansions of it).  A layer that reads another layer's latents has no c part (c_cache == nullptr).
+struct LatentTailParams {
+  const float* proj;      // [T][ldp]
+  int ldp, q_off, c_off, q_rank, kv_rank;
+  const float* wq;        // [q_rank]
+  const float* wc;        // [kv_rank]
+  void* cq_out;           // [T][q_rank]
+  void* c_cache;          // [pages][page_size][kv_rank]
+  const int32_t* row_req;
+  const int32_t* pos;
+  const int32_t* page_indptr;
+  const int32_t* page_indices;
+  int page_size;
+  float eps;
+};
+
+template <typename CT>
+__global__ void __launch_bounds__(128) latent_norm_append_kernel(LatentTailParams p) {
+  __shared__ float red[2][4];
+  pdl_sync();
+  const size_t t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float* q = p.proj + t * p.ldp + p.q_off;
+  const float* c = p.proj + t * p.ldp + p.c_off;
+  float sq = 0.f, sc = 0.f;
+  for (int i = threadIdx.x; i < p.q_rank; i += 128) sq = fmaf(q[i], q[i], sq);
+  if (p.c_cache)
+    for (int i = threadIdx.x; i < p.kv_rank; i += 128) sc = fmaf(c[i], c[i], sc);
+  sq = warp_sum(sq);
+  sc = warp_sum(sc);
+  if (lane == 0) { red[0][warp] = sq; red[1][warp] = sc; }
+  __syncthreads();
+  sq = red[0][0] + red[0][1] + red[0][2] + red[0][3];
+  sc = red[1][0] + red[1][1] + red[1][2] + red[1][3];
+  const float rq = 1.f / sqrtf(sq / p.q_rank + p.eps);
+  CT* qo = static_cast<CT*>(p.cq_out) + t * p.q_rank;
+  for (int i = threadIdx.x; i < p.q_rank; i += 128) qo[i] = wa_from_f<CT>(q[i] * rq * p.wq[i]);
+  if (p.c_cache == nullptr) return;
+  const float rc = 1.f / sqrtf(sc / p.kv_rank + p.eps);
+  const int b = p.row_req[t], ps = p.pos[t];
+  const size_t tok = static_cast<size_t>(p.page_indices[p.page_indptr[b] + ps / p.page_size]) * p.page_size + ps % p.page_size;
+  CT* co = static_cast<CT*>(p.c_cache) + tok * p.kv_rank;
+  for (int i = threadIdx.x; i < p.kv_rank; i += 128) co[i] = wa_from_f<CT>(c[i] * rc * p.wc[i]);
+}
+
 struct WindowAttnParams {
   const void* q;          // [T][H][dim]
   const void* k_cache;
@@ -713,6 +761,22 @@ int vb_qkv_rotary_append(const float* d_proj, int ldp, int q_off, int k_off, int
                   d_row_req, d_pos, d_page_indptr, d_page_indices, page_size, H, G, dim, vdim, vmix, d_v_first, d_lambda};
   if (dtype == 1) VB_LAUNCH_PDL(qkv_rotary_append_kernel<float>, T, 256, 0, stream, p);
   else VB_LAUNCH_PDL(qkv_rotary_append_kernel<bf16>, T, 256, 0, stream, p);
+  return 0;
+}
+
+int vb_latent_norm_append(const float* d_proj, int ldp, int q_off, int c_off, int q_rank, int kv_rank, const float* d_wq,
+                          const float* d_wc, void* d_cq_out, void* d_c_cache, const int32_t* d_row_req, const int32_t* d_pos,
+                          const int32_t* d_page_indptr, const int32_t* d_page_indices, int page_size, int T, float eps,
+                          int dtype, void* stream) {
+  VB_CHECK_ARG(d_proj && d_wq && d_cq_out && q_rank > 0 && q_off >= 0 && q_off + q_rank <= ldp,
+               "vb_latent_norm_append: bad query latent");
+  VB_CHECK_ARG(!d_c_cache || (d_wc && d_row_req && d_pos && d_page_indptr && d_page_indices && kv_rank > 0 && page_size > 0 &&
+                              c_off >= 0 && c_off + kv_rank <= ldp), "vb_latent_norm_append: bad key/value latent");
+  if (T <= 0) return 0;
+  LatentTailParams p{d_proj, ldp, q_off, c_off, q_rank, kv_rank, d_wq, d_wc, d_cq_out, d_c_cache, d_row_req, d_pos,
+                     d_page_indptr, d_page_indices, page_size, eps};
+  if (dtype == 1) VB_LAUNCH_PDL(latent_norm_append_kernel<float>, T, 128, 0, stream, p);
+  else VB_LAUNCH_PDL(latent_norm_append_kernel<bf16>, T, 128, 0, stream, p);
   return 0;
 }
 

@@ -1,7 +1,9 @@
 """Decoder stacks that mix softmax attention (sliding window, grouped heads, partial interleaved rotary, cross-layer
-value mixing, sigmoid output gate), linear attention with a per-head decay and a recurrent fp32 state, and
-mixture-of-experts feed-forwards with a shared expert, around an fp32 residual stream with LayerNorm before and after
-every sublayer.  ``LlamaEngine`` (engine.py) is the engine of the Llama-shaped speech LMs; this one is configured layer
+value mixing, sigmoid output gate), linear attention with a per-head decay and a recurrent fp32 state, latent attention
+(queries and keys/values through low-rank latents, only the key/value latent cached, optionally shared between layers)
+and dense or mixture-of-experts feed-forwards, around an fp32 residual stream.  Two block forms: ``sequential``
+(LayerNorm before and after every sublayer, mixer then feed-forward) and ``parallel`` (mixer and feed-forward read two
+RMS norms of the same stream and their sum is added, scaled; optionally followed by a per-token side input).  ``LlamaEngine`` (engine.py) is the engine of the Llama-shaped speech LMs; this one is configured layer
 by layer from a ``HybridConfig`` and runs the same way: a fixed sequence of C-ABI launches over preallocated buffers, no
 host synchronisation, CUDA-graph capturable.
 
@@ -9,8 +11,12 @@ One step serves a batch of requests that each bring one or more new tokens (a de
 of one).  Per layer:
     [fused q|k|v|gate projection]  ->  rotary + value mixing + page append  ->  window attention (* gate)  ->  o projection
     [fused q|k|v|gate projection]  ->  decay attention over the slot's state  ->  gated RMS norm         ->  o projection
+    [fused q-latent|kv-latent|gate projection] -> RMS norms + page append of the kv latent -> q up-projection -> queries
+        carried into latent space per head -> attention over the cached latents (one shared key = value head) -> per-head
+        value expansion * gate -> o projection
     router -> group by expert -> grouped gate/up (silu * up) -> grouped down -> shared expert -> weighted sum
-each followed by ``x += LayerNorm(y)`` fused with the LayerNorm that feeds the next sublayer.
+each followed (sequential form) by ``x += LayerNorm(y)`` fused with the LayerNorm that feeds the next sublayer, or
+(parallel form) by ``x += m * (mixer + feed-forward)`` fused with the side input and the next block's two RMS norms.
 
 Precision: ``dtype`` bfloat16 keeps projections' operands, q / k / v, the page cache and the attention output in bf16 with
 fp32 accumulation; norms, softmax, router, residual, recurrent state, decays and the lightning path after its projection
@@ -86,18 +92,44 @@ class DecayAttentionConfig:
 
 
 @dataclass
+class LatentAttentionConfig:
+    """Causal softmax attention without positional rotation whose queries go through a normed latent of q_rank dims and
+    whose keys and values are per-head expansions of ONE normed latent of kv_rank dims per token -- the only thing cached.
+    kv_from: the layer whose cached latents this layer reads instead of projecting its own.  One sigmoid gate per head."""
+    heads: int
+    dim: int
+    vdim: int
+    kv_rank: int
+    q_rank: int
+    scale: float
+    kv_from: Optional[int] = None
+
+
+@dataclass
+class DenseMLPConfig:
+    ff: int
+    act: str = "relu2"                    # "relu2" | "gelu" | "gelu_tanh": down(act(up h))
+
+
+@dataclass
 class MoEConfig:
     experts: int
     top: int
     ff: int
     shared_ff: int = 0                    # 0: no shared expert
+    act: str = "silu_glu"                 # "silu_glu": down(silu(gate h) * up h); else down(act(up h)) as DenseMLPConfig.act
+    router: str = "softmax"               # "softmax": top logits, softmax over the chosen.  "sigmoid": sigmoid scores, chosen
+    #                                       by score + correction within the kept groups, weights = chosen scores / their sum
+    groups: int = 0                       # sigmoid router: experts form this many groups of neighbours (0 / 1: one pool)
+    groups_keep: int = 0                  # ... of which the best this many stay eligible
+    shared_gate: bool = False             # the shared expert's output times sigmoid(w_sg . h)
 
 
 @dataclass
 class HybridLayerConfig:
-    kind: str                             # "attention" | "lightning"
+    kind: str                             # "attention" | "lightning" | "latent"
     mixer: Any
-    mlp: Optional[MoEConfig] = None
+    mlp: Any = None                       # MoEConfig | DenseMLPConfig | None
 
 
 @dataclass
@@ -107,6 +139,12 @@ class HybridConfig:
     eps: float
     logit_scale: float
     layers: List[HybridLayerConfig]
+    block: str = "sequential"             # "sequential": x += LN(mixer(LN x)); x += LN(ff(LN x)).  "parallel": x += m * (mixer(n1 x) + ff(n2 x))
+    norm: str = "layernorm"               # "layernorm" (weight and bias) | "rmsnorm" (weight)
+    residual_mult: float = 1.0            # m of the parallel form
+    positions: int = 0                    # rows of the learned position table added to the embedding (0: none)
+    side_dim: int = 0                     # per-token side input of every block (parallel form): dims per layer (0: none)
+    logit_softcap: float = 0.0            # logits <- cap * tanh(logits / cap) (0: none)
 
     @classmethod
     def from_json(cls, c: Dict[str, Any]) -> "HybridConfig":
@@ -187,19 +225,43 @@ class HybridWeights:
                 return ops.pack_weight(ops.interleave_gate_up(mat(gate_name), mat(up_name), half), 2 * half)
             return mat(gate_name, up_name)
 
+        self._mat, self._vec, self._dense = mat, vec, dense
+        rms = cfg.norm == "rmsnorm"
+        if rms:
+            norm = lambda name: (vec(name), None)                      # noqa: E731
         self.embed = mat("embed")
         self.head = dense(mat("head"))
         self.final_norm = norm("final.norm")
         # the tcgen05 kernel has no output scale: logit_scale is folded into the final norm's weight and bias there
-        self.final_norm_scaled = tuple(t * cfg.logit_scale for t in self.final_norm)
+        self.final_norm_scaled = tuple(t * cfg.logit_scale if t is not None else None for t in self.final_norm)
         if tuple(self.embed.shape) != (cfg.vocab, cfg.width) or tuple(sd["head"].shape) != (cfg.vocab, cfg.width):
             raise VoxB200Error("embed / head shapes do not match the configuration")
+        self.pos = self.side_embed = None
+        if cfg.positions:
+            self.pos = mat("pos")
+            if tuple(self.pos.shape) != (cfg.positions, cfg.width):
+                raise VoxB200Error("position table shape does not match the configuration")
+        if cfg.side_dim:
+            self.side_embed = mat("side.embed")
+            if tuple(self.side_embed.shape) != (cfg.vocab, cfg.side_dim * len(cfg.layers)):
+                raise VoxB200Error("side embedding shape does not match the configuration")
         self.layers: List[Dict[str, Any]] = []
         for i, L in enumerate(cfg.layers):
             p = f"l{i}."
-            w: Dict[str, Any] = {"norm1": norm(p + "norm1"), "norm1b": norm(p + "norm1b")}
             m = L.mixer
-            if L.kind == "attention":
+            if cfg.block == "parallel":
+                w: Dict[str, Any] = {"norm1": vec(p + "norm1")}
+                if L.mlp is not None:
+                    w["norm2"] = vec(p + "norm2")
+                if cfg.side_dim:
+                    w["side_gate"], w["side_proj"], w["side_norm"] = mat(p + "side.gate"), mat(p + "side.proj"), vec(p + "side.norm")
+                    if tuple(w["side_gate"].shape) != (cfg.side_dim, cfg.width) or tuple(w["side_proj"].shape) != (cfg.width, cfg.side_dim):
+                        raise VoxB200Error(f"layer {i}: side input shapes do not match the configuration")
+            else:
+                w = {"norm1": norm(p + "norm1"), "norm1b": norm(p + "norm1b")}
+            if L.kind == "latent":
+                self._load_latent(sd, p, i, m, w)
+            elif L.kind == "attention":
                 w["qkvg"] = mat(p + "mix.q", p + "mix.k", p + "mix.v", p + "mix.g")
                 w["o"] = mat(p + "mix.o")
                 if m.v_mix:
@@ -211,12 +273,21 @@ class HybridWeights:
                 w["norm"] = vec(p + "mix.norm")
                 w["decay"] = torch.tensor(m.decay, dtype=torch.float64).to(device=dev, dtype=F32)
                 want = 2 * m.heads * m.dim + 2 * m.heads * m.vdim
-            if tuple(w["qkvg"].shape) != (want, cfg.width):
-                raise VoxB200Error(f"layer {i}: projection shapes {tuple(w['qkvg'].shape)} do not match the configuration")
-            w["qkvg"], w["o"] = dense(w["qkvg"]), dense(w["o"])
-            if L.mlp is not None:
+            if L.kind != "latent":
+                if tuple(w["qkvg"].shape) != (want, cfg.width):
+                    raise VoxB200Error(f"layer {i}: projection shapes {tuple(w['qkvg'].shape)} do not match the configuration")
+                w["qkvg"], w["o"] = dense(w["qkvg"]), dense(w["o"])
+            if isinstance(L.mlp, DenseMLPConfig):
+                w["up"], w["down"] = mat(p + "mlp.up"), mat(p + "mlp.down")
+                if tuple(w["up"].shape) != (L.mlp.ff, cfg.width) or tuple(w["down"].shape) != (cfg.width, L.mlp.ff):
+                    raise VoxB200Error(f"layer {i}: feed-forward shapes do not match the configuration")
+                w["up"], w["down"] = dense(w["up"]), dense(w["down"])
+            elif L.mlp is not None and L.mlp.act != "silu_glu":
+                self._load_plain_moe(sd, p, i, L.mlp, w)
+            elif L.mlp is not None:
                 f = L.mlp
-                w["norm2"], w["norm2b"] = norm(p + "norm2"), norm(p + "norm2b")
+                if cfg.block != "parallel":
+                    w["norm2"], w["norm2b"] = norm(p + "norm2"), norm(p + "norm2b")
                 w["router"] = vec(p + "mlp.router")
                 w["router_b"] = vec(p + "mlp.router.b") if (p + "mlp.router.b") in sd else None
                 n_all = f.experts * f.ff + f.shared_ff
@@ -245,6 +316,62 @@ class HybridWeights:
                         w["s_gu"] = gate_up(p + "mlp.shared.gate", p + "mlp.shared.up")
                         w["s_down"] = dense(mat(p + "mlp.shared.down"))
             self.layers.append(w)
+        del self._mat, self._vec, self._dense
+
+    def _load_latent(self, sd, p: str, i: int, m: "LatentAttentionConfig", w: Dict[str, Any]) -> None:
+        """``l<i>.mix.{dq, dq.norm, uq, dkv, dkv.norm, uk, uv, g, o}``: dq | dkv | g become one projection (a layer that
+        reads another layer's latents has no dkv); uk is kept per head and transposed ([H, kv_rank, dim]: it carries a
+        head's query into latent space), uv per head ([H, vdim, kv_rank]: it expands a head's latent-space output)."""
+        mat, vec, dense, W = self._mat, self._vec, self._dense, self.cfg.width
+        own = m.kv_from is None
+        if not own:
+            src = self.cfg.layers[m.kv_from] if 0 <= m.kv_from < i else None
+            if src is None or src.kind != "latent" or src.mixer.kv_from is not None or src.mixer.kv_rank != m.kv_rank:
+                raise VoxB200Error(f"layer {i}: kv_from {m.kv_from} must name an earlier latent-attention layer that "
+                                   "projects its own latents of the same rank")
+        names = [p + "mix.dq"] + ([p + "mix.dkv"] if own else []) + [p + "mix.g"]
+        down = mat(*names)
+        if tuple(down.shape) != (m.q_rank + (m.kv_rank if own else 0) + m.heads, W):
+            raise VoxB200Error(f"layer {i}: latent projection shapes do not match the configuration")
+        uq, uk, uv, o = mat(p + "mix.uq"), mat(p + "mix.uk"), mat(p + "mix.uv"), mat(p + "mix.o")
+        if (tuple(uq.shape) != (m.heads * m.dim, m.q_rank) or tuple(uk.shape) != (m.heads * m.dim, m.kv_rank) or
+                tuple(uv.shape) != (m.heads * m.vdim, m.kv_rank) or tuple(o.shape) != (W, m.heads * m.vdim)):
+            raise VoxB200Error(f"layer {i}: latent attention shapes do not match the configuration")
+        w["lat_in"], w["uq"], w["o"] = dense(down), dense(uq), dense(o)
+        w["dq_norm"] = vec(p + "mix.dq.norm")
+        if own:
+            w["dkv_norm"] = vec(p + "mix.dkv.norm")
+        w["uk_t"] = uk.view(m.heads, m.dim, m.kv_rank).transpose(1, 2).contiguous()
+        w["uv"] = uv.view(m.heads, m.vdim, m.kv_rank).contiguous()
+
+    def _load_plain_moe(self, sd, p: str, i: int, f: "MoEConfig", w: Dict[str, Any]) -> None:
+        """Experts of the form down(act(up h)): ``l<i>.mlp.{router, correction, e<j>.{up, down}, shared.{up, down, sg}}``.
+        On tensor-core projections every expert and the shared expert are stacked into ONE up matrix (along N) and ONE down
+        matrix (along K); otherwise the experts are [E, ...] stacks for the grouped linear kernel."""
+        mat, vec, dense, W = self._mat, self._vec, self._dense, self.cfg.width
+        w["router"] = vec(p + "mlp.router")
+        w["correction"] = vec(p + "mlp.correction") if (p + "mlp.correction") in sd else None
+        if tuple(w["router"].shape) != (f.experts, W):
+            raise VoxB200Error(f"layer {i}: router shape does not match the configuration")
+        if f.shared_ff and f.shared_gate:
+            w["sg"] = vec(p + "mlp.shared.sg").reshape(-1)
+        names = [f"e{e}" for e in range(f.experts)] + (["shared"] if f.shared_ff else [])
+        n_all = f.experts * f.ff + f.shared_ff
+        if self.tensor_core and W % 8 == 0 and n_all % 8 == 0 and f.experts <= self.DENSE_MOE_MAX_RATIO * f.top:
+            fit = [r for r in (128, 64, 32, 16) if f.ff % r == 0 and f.shared_ff % r == 0]
+            tr = fit[0] if fit else 128
+            w["up_all"] = ops.pack_weight(torch.cat([mat(p + f"mlp.{n}.up") for n in names], 0).contiguous(), tr)
+            w["down_all"] = ops.pack_weight(torch.cat([mat(p + f"mlp.{n}.down") for n in names], 1).contiguous(), 128)
+            if fit and f.ff % 64 == 0:
+                gb = ops.weight_tiles_bytes(f.ff, W, tr)
+                w["grouped"] = {"group_bytes": gb, "kb_total": (n_all + 63) // 64, "group_kb": f.ff // 64}
+                if f.shared_ff:
+                    w["s_up_view"] = ops.PackedWeight(w["up_all"].data[f.experts * gb:], f.shared_ff, W, tr)
+        else:
+            w["up"] = torch.stack([mat(p + f"mlp.e{e}.up") for e in range(f.experts)]).contiguous()
+            w["down"] = torch.stack([mat(p + f"mlp.e{e}.down") for e in range(f.experts)]).contiguous()
+            if f.shared_ff:
+                w["s_up"], w["s_down"] = dense(mat(p + "mlp.shared.up")), dense(mat(p + "mlp.shared.down"))
 
     # the dense mixture-of-experts form runs experts / top times the FLOPs a token needs: taken up to this ratio
     DENSE_MOE_MAX_RATIO = 8
@@ -264,8 +391,8 @@ class HybridWeights:
             elif isinstance(o, dict):
                 for x in o.values():
                     walk(x)
-        walk([self.embed, self.head, self.final_norm,
-              [{k: v for k, v in L.items() if k != "s_gu_view"} for L in self.layers]])      # (views of other entries)
+        walk([self.embed, self.head, self.final_norm, self.pos, self.side_embed,
+              [{k: v for k, v in L.items() if k not in ("s_gu_view", "s_up_view")} for L in self.layers]])   # (views of other entries)
         return n
 
 
@@ -274,8 +401,9 @@ class HybridWeights:
 # ------------------------------------------------------------------------------------------------------------------
 class HybridCache:
     """Per attention layer K [pages, page, G, dim] and V [pages, page, G, vdim] in the compute dtype (all layers share
-    one page table: page p of every layer belongs to the same request); per linear-attention layer a state
-    [slots, H, dim, vdim] in fp32.  Pages and slots are handed out by the worker; a slot's state is treated as zero by
+    one page table: page p of every layer belongs to the same request); per latent-attention layer that projects its own
+    latents ONE tensor [pages, page, 1, kv_rank] that is both K and V (a layer reading another layer's latents aliases
+    that layer's tensor); per linear-attention layer a state [slots, H, dim, vdim] in fp32.  Pages and slots are handed out by the worker; a slot's state is treated as zero by
     the kernels when its request starts at position 0, so nothing is cleared on reuse."""
 
     def __init__(self, cfg: HybridConfig, num_pages: int, page_size: int, num_slots: int, dtype: torch.dtype, device):
@@ -288,11 +416,17 @@ class HybridCache:
             if L.kind == "attention":
                 self.k[i] = torch.zeros(num_pages, page_size, m.kv_heads, m.dim, dtype=dtype, device=device)
                 self.v[i] = torch.zeros(num_pages, page_size, m.kv_heads, m.vdim, dtype=dtype, device=device)
+            elif L.kind == "latent":
+                if m.kv_from is None:
+                    self.k[i] = self.v[i] = torch.zeros(num_pages, page_size, 1, m.kv_rank, dtype=dtype, device=device)
+                else:
+                    self.k[i] = self.v[i] = self.k[m.kv_from]
             else:
                 self.state[i] = torch.zeros(num_slots, m.heads, m.dim, m.vdim, dtype=F32, device=device)
 
     def nbytes(self) -> int:
-        return sum(t.numel() * t.element_size() for d in (self.k, self.v, self.state) for t in d.values())
+        seen = {t.data_ptr(): t for d in (self.k, self.v, self.state) for t in d.values()}      # (aliases count once)
+        return sum(t.numel() * t.element_size() for t in seen.values())
 
 
 @dataclass
@@ -328,15 +462,31 @@ class HybridEngine:
         dev, R, W, CT = weights.device, max_rows, cfg.width, weights.dtype
         att = [L.mixer for L in cfg.layers if L.kind == "attention"]
         lin = [L.mixer for L in cfg.layers if L.kind == "lightning"]
-        moe = [L.mlp for L in cfg.layers if L.mlp is not None]
+        lat = [L.mixer for L in cfg.layers if L.kind == "latent"]
+        moe = [L.mlp for L in cfg.layers if isinstance(L.mlp, MoEConfig)]
+        dmlp = [L.mlp for L in cfg.layers if isinstance(L.mlp, DenseMLPConfig)]
         p_att = [m.heads * m.dim + m.kv_heads * (m.dim + m.vdim) + m.heads * m.vdim for m in att]
         p_lin = [2 * m.heads * (m.dim + m.vdim) for m in lin]
-        hv = max([m.heads * m.vdim for m in att + lin] + [1])
+        p_lat = [m.q_rank + m.kv_rank + m.heads for m in lat]
+        hv = max([m.heads * m.vdim for m in att + lin + lat] + [1])
+        for m in lat:
+            if m.kv_rank > 256:
+                raise VoxB200Error(f"latent attention: kv_rank {m.kv_rank} exceeds the 256 dims the attention kernels take per head")
         self.x = torch.zeros(R, W, dtype=F32, device=dev)              # residual stream
         self.h = torch.zeros(R, W, dtype=CT, device=dev)               # normed input of the running sublayer
         self.y = torch.zeros(R, W, dtype=F32, device=dev)              # sublayer output
-        self.proj = torch.zeros(R * max(p_att + p_lin + [1]), dtype=F32, device=dev)
-        self.q = torch.zeros(R * max([m.heads * m.dim for m in att] + [1]), dtype=CT, device=dev)
+        self.proj = torch.zeros(R * max(p_att + p_lin + p_lat + [1]), dtype=F32, device=dev)
+        self.q = torch.zeros(R * max([m.heads * m.dim for m in att + lat] + [1]), dtype=CT, device=dev)
+        if cfg.block == "parallel":
+            self.h2 = torch.zeros(R, W, dtype=CT, device=dev)          # the feed-forward's norm of the same stream
+            self.y2 = torch.zeros(R, W, dtype=F32, device=dev)         # the feed-forward's output
+        if lat:
+            self.cq = torch.zeros(R * max(m.q_rank for m in lat), dtype=CT, device=dev)            # normed query latent
+            n_lat = R * max(m.heads * m.kv_rank for m in lat)
+            self.q_lat = torch.zeros(n_lat, dtype=CT, device=dev)      # queries carried into latent space
+            self.o_lat = torch.zeros(n_lat, dtype=CT, device=dev)      # attention output in latent space
+        if dmlp:
+            self.ff_act = torch.zeros(R * max(f.ff for f in dmlp), dtype=CT, device=dev)
         self.mix_out = torch.zeros(R * hv, dtype=CT, device=dev)       # gated mixer output, input of the o projection
         self.lin_o = torch.zeros(R * hv, dtype=F32, device=dev)        # linear-attention output before its norm
         # scratch of the sequence-parallel linear attention: one state per tile of 64 rows (a step has at most
@@ -349,7 +499,8 @@ class HybridEngine:
             self.lin_scratch = torch.zeros(n_t * max(m.heads * m.dim * m.vdim for m in tiled), dtype=F32, device=dev)
         self.v_first = torch.zeros(R * max([m.kv_heads * m.vdim for m in att if m.v_mix] + [1]), dtype=F32, device=dev)
         # split-key scratch of the per-row attention kernel: steps of up to 256 rows, 8 splits
-        self.attn_part = torch.zeros(256 * 8 * max([m.heads * (m.vdim + 2) for m in att] + [1]), dtype=F32, device=dev)
+        self.attn_part = torch.zeros(256 * 8 * max([m.heads * (m.vdim + 2) for m in att] +
+                                                   [m.heads * (m.kv_rank + 2) for m in lat] + [1]), dtype=F32, device=dev)
         self.freqs: Dict[Tuple, torch.Tensor] = {}
         self.cs: Dict[Tuple, torch.Tensor] = {}
         for m in att:
@@ -375,6 +526,7 @@ class HybridEngine:
             self.moe_out = torch.zeros(rmax * W, dtype=F32, device=dev)
             self.s_act = torch.zeros(R * max([f.shared_ff for f in moe] + [1]), dtype=CT, device=dev)
             self.s_out = torch.zeros(R, W, dtype=F32, device=dev)
+            self.moe_sgate = torch.zeros(R, dtype=F32, device=dev)     # the shared expert's per-token gate
         self.sms = ops.device_info()[0] if dev.type == "cuda" else 1
         self.partials = torch.zeros(2 * self.sms * 128 * 256 if weights.tensor_core else 4, dtype=F32, device=dev)
         self.hn = torch.zeros(max_out_rows, W, dtype=CT, device=dev)
@@ -404,7 +556,52 @@ class HybridEngine:
             return out
         return ops.linear(x, w, out, alpha=alpha)
 
+    def _proj_ct(self, x: torch.Tensor, w, out: torch.Tensor, act: Optional[str] = None) -> torch.Tensor:
+        """out (compute dtype) = act(x @ w^T): the activation runs in the projection's epilogue on the fp32 sum."""
+        if isinstance(w, ops.PackedWeight):
+            return ops.gemm(x, w, mode=0, out=out, tile_rows=w.tile_rows, act=act)
+        return ops.linear(x, w, out, epilogue=ops.LINEAR_ACTS[act])
+
     # ---- mixers ----------------------------------------------------------------------------------------------
+    def _run_attention(self, s: StepInputs, q, kc, vc, out, gate, H: int, G: int, dim: int, vdim: int, window: int,
+                       scale: float) -> None:
+        """Prompt portions on the tiled kernel and single-token rows on the per-row kernel (split over keys with few rows)."""
+        tiles = None
+        if s.tiles is not None and self.use_tiled_attention and vdim <= 256:
+            tiles = (s.qo_indptr, s.tiles[0], s.tiles[1], s.tiles[2])
+        args = (q, kc, vc, out, gate, s.row_req, s.pos, s.page_indptr, s.page_indices, s.T, H, G, dim, vdim, window, scale)
+        if tiles is not None and (not s.single or s.single_rows is not None):
+            ops.window_attn(*args, tiles=tiles)
+            if s.single:
+                ops.window_attn(*args, scratch=self.attn_part, rows=s.single_rows)
+        else:
+            ops.window_attn(*args, scratch=self.attn_part)
+
+    def _latent(self, i: int, m: LatentAttentionConfig, w: Dict[str, Any], s: StepInputs) -> torch.Tensor:
+        """Latent attention in its absorbed form: a head's score q . (U_k c) equals (U_k^T q) . c and its output
+        U_v (sum_j p_j c_j), so the cached latents serve every head directly as one shared key = value head of kv_rank
+        dims, and neither keys nor values are ever formed per token."""
+        T, H, R = s.T, m.heads, m.kv_rank
+        own = m.kv_from is None
+        P = m.q_rank + (R if own else 0) + H
+        proj = self._proj(self.h[:T], w["lat_in"], self.proj[:T * P].view(T, P))
+        cq = self.cq[:T * m.q_rank].view(T, m.q_rank)
+        cache = self.cache.k[i]
+        ops.latent_norm_append(proj, 0, m.q_rank, m.q_rank, R, w["dq_norm"], w.get("dkv_norm"), cq, cache if own else None,
+                               s.row_req, s.pos, s.page_indptr, s.page_indices, T, self.cfg.eps)
+        q = self._proj_ct(cq, w["uq"], self.q[:T * H * m.dim].view(T, H * m.dim))
+        q_lat = ops.linear_batched(q.view(T, H, m.dim), w["uk_t"], self.q_lat[:T * H * R].view(T, H, R))
+        o_lat = self.o_lat[:T * H * R].view(T, H * R)
+        self._run_attention(s, q_lat.view(T, H * R), cache, cache, o_lat, None, H, 1, R, R, 0, m.scale)
+        out = self.mix_out[:T * H * m.vdim].view(T, H, m.vdim)
+        ops.linear_batched(o_lat.view(T, H, R), w["uv"], out, gate=proj[:, P - H:])
+        return self._proj(out.view(T, H * m.vdim), w["o"], self.y[:T])
+
+    def _dense_mlp(self, f: DenseMLPConfig, w: Dict[str, Any], h: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        T = h.shape[0]
+        act = self._proj_ct(h, w["up"], self.ff_act[:T * f.ff].view(T, f.ff), act=f.act)
+        return self._proj(act, w["down"], out)
+
     def _attention(self, i: int, m: WindowAttentionConfig, w: Dict[str, Any], s: StepInputs) -> torch.Tensor:
         T, W = s.T, self.cfg.width
         nq, nk, nv = m.heads * m.dim, m.kv_heads * m.dim, m.kv_heads * m.vdim
@@ -420,19 +617,8 @@ class HybridEngine:
                               self.v_first if m.v_mix else None, w.get("vmix") if vmix == 2 else None)
         out = self.mix_out[:T * m.heads * m.vdim].view(T, m.heads * m.vdim)
         gate = proj[:, nq + nk + nv:] if m.gate else None
-        tiles = None
-        if s.tiles is not None and self.use_tiled_attention and m.vdim <= 256:
-            tiles = (s.qo_indptr, s.tiles[0], s.tiles[1], s.tiles[2])
-        args = (q, self.cache.k[i], self.cache.v[i], out, gate, s.row_req, s.pos, s.page_indptr, s.page_indices, T, m.heads,
-                m.kv_heads, m.dim, m.vdim, m.window, m.scale)
-        if tiles is not None and (not s.single or s.single_rows is not None):
-            # prompt portions on the tiled kernel; in a mixed step the single-token rows on the per-row kernel
-            ops.window_attn(*args, tiles=tiles)
-            if s.single:
-                ops.window_attn(*args, scratch=self.attn_part, rows=s.single_rows)
-        else:
-            # decode steps (and steps without tiles) on the per-row kernel
-            ops.window_attn(*args, scratch=self.attn_part)
+        self._run_attention(s, q, self.cache.k[i], self.cache.v[i], out, gate, m.heads, m.kv_heads, m.dim, m.vdim, m.window,
+                            m.scale)
         return self._proj(out, w["o"], self.y[:T])
 
     def _lightning(self, i: int, m: DecayAttentionConfig, w: Dict[str, Any], s: StepInputs) -> torch.Tensor:
@@ -454,9 +640,58 @@ class HybridEngine:
         ops.gated_rmsnorm(o, w["norm"], proj[:, 2 * nq + nv:], self.cfg.eps, out)
         return self._proj(out, w["o"], self.y[:T])
 
-    def _moe(self, f: MoEConfig, w: Dict[str, Any], s: StepInputs) -> torch.Tensor:
+    def _moe_plain(self, f: MoEConfig, w: Dict[str, Any], s: StepInputs, h: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """Experts of the form down(act(up h)) behind the sigmoid router; the shared expert enters times its per-token gate."""
         T, W = s.T, self.cfg.width
-        h = self.h[:T]
+        idx, wts = self.moe_idx[:T * f.top], self.moe_wts[:T * f.top]
+        sgate = self.moe_sgate[:T] if (f.shared_ff and f.shared_gate) else None
+        ops.moe_route_sigmoid(h, w["router"], w.get("correction"), f.top, idx, wts, f.groups, f.groups_keep,
+                              w.get("sg") if sgate is not None else None, sgate)
+        if "grouped" in w and T >= self.GROUPED_MIN_ROWS:
+            g, tt = w["grouped"], self.GROUP_TILE
+            n_tiles = (T * f.top + tt - 1) // tt + f.experts
+            rows = n_tiles * tt
+            ops.moe_group(idx, T, f.experts, f.top, self.moe_row_off, self.moe_sorted, self.moe_pair_row, tile_rows=tt,
+                          tile_group=self.moe_tile_group[:n_tiles])
+            xs = ops.moe_gather_rows(h, self.moe_sorted, self.moe_xs[:rows * W].view(rows, W))
+            act = self.moe_act[:rows * f.ff].view(rows, f.ff)
+            ops.gemm_grouped(xs, w["up_all"], act, 0, f.ff, W, tt, self.moe_tile_group, group_bytes=g["group_bytes"], act=f.act)
+            eo = self.moe_out[:rows * W].view(rows, W)
+            ops.gemm_grouped(act, w["down_all"], eo, 1, W, f.ff, tt, self.moe_tile_group, w_kb_stride=g["kb_total"],
+                             group_kb=g["group_kb"])
+            shared = None
+            if f.shared_ff:
+                sa = self.s_act[:T * f.shared_ff].view(T, f.shared_ff)
+                ops.gemm(h, w["s_up_view"], mode=0, out=sa, tile_rows=w["s_up_view"].tile_rows, act=f.act)
+                shared = ops.gemm_grouped(sa, w["down_all"], self.s_out[:T], 1, W, f.shared_ff, ops.gemm_t_tile(T), None,
+                                          w_kb_stride=g["kb_total"], kb_base=f.experts * g["group_kb"])
+            return ops.moe_combine(eo, shared, wts, self.moe_pair_row, f.top, out, shared_scale=sgate)
+        if "up_all" in w:
+            # dense form: every expert on every token as one stacked up and one stacked down projection; in between the
+            # columns of an expert take the token's routing weight (or zero), the shared expert's columns its gate
+            n_all = f.experts * f.ff + f.shared_ff
+            act = self.moe_act[:T * n_all].view(T, n_all)
+            ops.gemm(h, w["up_all"], mode=0, out=act, tile_rows=w["up_all"].tile_rows, act=f.act)
+            ops.moe_scale_dense(act, idx, wts, f.experts, f.ff, f.top, sgate, f.shared_ff)
+            return self._proj(act, w["down_all"], out)
+        ops.moe_group(idx, T, f.experts, f.top, self.moe_row_off, self.moe_sorted, self.moe_pair_row)
+        act = self.moe_act[:T * f.top * f.ff].view(T * f.top, f.ff)
+        ops.linear(h, w["up"], act, epilogue=ops.LINEAR_ACTS[f.act], row_off=self.moe_row_off, gather=self.moe_sorted, rows=T)
+        eo = self.moe_out[:T * f.top * W].view(T * f.top, W)
+        ops.linear(act, w["down"], eo, row_off=self.moe_row_off, rows=T)
+        shared = None
+        if f.shared_ff:
+            sa = self._proj_ct(h, w["s_up"], self.s_act[:T * f.shared_ff].view(T, f.shared_ff), act=f.act)
+            shared = self._proj(sa, w["s_down"], self.s_out[:T])
+        return ops.moe_combine(eo, shared, wts, self.moe_pair_row, f.top, out, shared_scale=sgate)
+
+    def _moe(self, f: MoEConfig, w: Dict[str, Any], s: StepInputs, h: Optional[torch.Tensor] = None,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        T, W = s.T, self.cfg.width
+        h = self.h[:T] if h is None else h
+        out = self.y[:T] if out is None else out
+        if f.act != "silu_glu":
+            return self._moe_plain(f, w, s, h, out)
         idx, wts = self.moe_idx[:T * f.top], self.moe_wts[:T * f.top]
         ops.moe_route(h, w["router"], w["router_b"], f.top, idx, wts)
         if "grouped" in w and T >= self.GROUPED_MIN_ROWS:
@@ -480,13 +715,13 @@ class HybridEngine:
                 ops.gemm(h, w["s_gu_view"], mode=2, out=sa, tile_rows=w["s_gu_view"].tile_rows, n_out=f.shared_ff)
                 shared = ops.gemm_grouped(sa, w["down_all"], self.s_out[:T], 1, W, f.shared_ff, ops.gemm_t_tile(T), None,
                                           w_kb_stride=g["kb_total"], kb_base=f.experts * g["group_kb"])
-            return ops.moe_combine(eo, shared, wts, self.moe_pair_row, f.top, self.y[:T])
+            return ops.moe_combine(eo, shared, wts, self.moe_pair_row, f.top, out)
         if "gu_all" in w:
             n_all = f.experts * f.ff + f.shared_ff
             act = self.moe_act[:T * n_all].view(T, n_all)
             ops.gemm(h, w["gu_all"], mode=2, out=act, tile_rows=w["gu_all"].tile_rows, n_out=n_all)
             ops.moe_scale_dense(act, idx, wts, f.experts, f.ff, f.top)
-            return self._proj(act, w["down_all"], self.y[:T])
+            return self._proj(act, w["down_all"], out)
         ops.moe_group(idx, T, f.experts, f.top, self.moe_row_off, self.moe_sorted, self.moe_pair_row)
         act = self.moe_act[:T * f.top * f.ff].view(T * f.top, f.ff)
         ops.linear(h, w["gu"], act, epilogue=1, row_off=self.moe_row_off, gather=self.moe_sorted, rows=T)
@@ -500,7 +735,7 @@ class HybridEngine:
             else:
                 ops.linear(h, w["s_gu"], sa, epilogue=1)
             shared = self._proj(sa, w["s_down"], self.s_out[:T])
-        return ops.moe_combine(eo, shared, wts, self.moe_pair_row, f.top, self.y[:T])
+        return ops.moe_combine(eo, shared, wts, self.moe_pair_row, f.top, out)
 
     # ---- the step --------------------------------------------------------------------------------------------
     def forward(self, s: StepInputs) -> torch.Tensor:
@@ -509,8 +744,10 @@ class HybridEngine:
         cfg, w, T = self.cfg, self.w, s.T
         if T > self.max_rows or s.n_out > self.max_out_rows:
             raise VoxB200Error(f"step of {T} rows / {s.n_out} logit rows exceeds the engine's {self.max_rows} / {self.max_out_rows}")
+        if cfg.block == "parallel":
+            return self._forward_parallel(s)
         x, h, y = self.x[:T], self.h[:T], self.y[:T]
-        ops.embed_rows_f32(w.embed, s.ids, x)
+        ops.embed_rows_f32(w.embed, s.ids, x, w.pos, s.pos if w.pos is not None else None)
         for key, freq in self.freqs.items():
             ops.rotary_table(s.pos, freq, self.cs[key][:T])
         eps = cfg.eps
@@ -520,10 +757,7 @@ class HybridEngine:
         for i, L in enumerate(cfg.layers):
             lw = w.layers[i]
             # (a sublayer hands back its output [T, W], or the split-K planes of its last projection [split, T, W])
-            if L.kind == "attention":
-                ym = self._attention(i, L.mixer, lw, s)
-            else:
-                ym = self._lightning(i, L.mixer, lw, s)
+            ym = self._mixer(i, L, lw, s)
             nxt = w.layers[i + 1]["norm1"] if i + 1 < n else None
             if L.mlp is not None:
                 ops.postnorm_residual_f32(x, ym, *lw["norm1b"], eps, h, *lw["norm2"])
@@ -533,9 +767,54 @@ class HybridEngine:
                 ops.postnorm_residual_f32(x, ym, *lw["norm1b"], eps, *((h,) + nxt if nxt else (None, None, None)))
             if self.layer_tap is not None:
                 self.layer_tap.append(x.clone())
+        return self._head(s)
+
+    def _mixer(self, i: int, L: HybridLayerConfig, lw: Dict[str, Any], s: StepInputs) -> torch.Tensor:
+        if L.kind == "attention":
+            return self._attention(i, L.mixer, lw, s)
+        if L.kind == "latent":
+            return self._latent(i, L.mixer, lw, s)
+        return self._lightning(i, L.mixer, lw, s)
+
+    def _head(self, s: StepInputs) -> torch.Tensor:
+        """Final norm of the rows whose logits are wanted, output head, logit scale, soft cap."""
+        cfg, w = self.cfg, self.w
         hn = self.hn[:s.n_out]
-        if isinstance(w.head, ops.PackedWeight):
-            ops.layernorm_f32(self.x, *w.final_norm_scaled, eps, hn, rows=s.out_rows)
-            return self._proj(hn, w.head, self.logits[:s.n_out])
-        ops.layernorm_f32(self.x, *w.final_norm, eps, hn, rows=s.out_rows)
-        return self._proj(hn, w.head, self.logits[:s.n_out], alpha=cfg.logit_scale)
+        packed = isinstance(w.head, ops.PackedWeight)
+        nw, nb = w.final_norm_scaled if packed else w.final_norm
+        if cfg.norm == "rmsnorm":
+            ops.rmsnorm2_f32(self.x, nw, cfg.eps, hn, rows=s.out_rows)
+        else:
+            ops.layernorm_f32(self.x, nw, nb, cfg.eps, hn, rows=s.out_rows)
+        logits = self._proj(hn, w.head, self.logits[:s.n_out], alpha=1.0 if packed else cfg.logit_scale)
+        if cfg.logit_softcap:
+            ops.softcap_f32(logits, cfg.logit_softcap)
+        return logits
+
+    def _forward_parallel(self, s: StepInputs) -> torch.Tensor:
+        """Blocks whose mixer and feed-forward read two RMS norms of the same stream:
+        x += m * (mixer(norm1 x) + ff(norm2 x)), then the per-token side input, fused with the next block's norms."""
+        cfg, w, T = self.cfg, self.w, s.T
+        x, h1, h2, eps = self.x[:T], self.h[:T], self.h2[:T], cfg.eps
+        ops.embed_rows_f32(w.embed, s.ids, x, w.pos, s.pos if w.pos is not None else None)
+        n = len(cfg.layers)
+        if n:
+            ops.rmsnorm2_f32(x, w.layers[0]["norm1"], eps, h1, w.layers[0].get("norm2"), h2 if "norm2" in w.layers[0] else None)
+        for i, L in enumerate(cfg.layers):
+            lw = w.layers[i]
+            ym = self._mixer(i, L, lw, s)
+            yf = None
+            if isinstance(L.mlp, DenseMLPConfig):
+                yf = self._dense_mlp(L.mlp, lw, h2, self.y2[:T])
+            elif L.mlp is not None:
+                yf = self._moe(L.mlp, lw, s, h=h2, out=self.y2[:T])
+            side = None
+            if cfg.side_dim:
+                side = (lw["side_gate"], lw["side_proj"], lw["side_norm"], w.side_embed, i * cfg.side_dim, s.ids)
+            nxt = w.layers[i + 1] if i + 1 < n else None
+            ops.residual_side_f32(x, ym, yf, cfg.residual_mult, eps, side,
+                                  out1=h1 if nxt else None, w1=nxt["norm1"] if nxt else None,
+                                  out2=h2 if nxt and "norm2" in nxt else None, w2=nxt.get("norm2") if nxt else None)
+            if self.layer_tap is not None:
+                self.layer_tap.append(x.clone())
+        return self._head(s)

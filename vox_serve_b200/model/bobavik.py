@@ -95,6 +95,17 @@ def synthetic_state_dict(cfg: HybridConfig, seed: int = 0, device="cpu") -> Dict
 class BobavikModel(BaseLM):
     is_text_model = True
     has_recurrent_state = True
+    design = "Bobavik"
+    synthetic_name = "bobavik-synthetic"
+
+    # what a design built on the hybrid engine supplies: its configuration reader and its seeded random weights
+    @staticmethod
+    def read_config(config: Dict[str, Any]) -> HybridConfig:
+        return HybridConfig.from_json(config)
+
+    @staticmethod
+    def synthetic_weights(cfg: HybridConfig, seed: int, device) -> Dict[str, torch.Tensor]:
+        return synthetic_state_dict(cfg, seed, device)
 
     def __init__(self, model_name: str, dtype: torch.dtype = torch.bfloat16, device: str = "cuda:0",
                  enable_torch_compile: bool = False, audio_decoder_device: Optional[str] = None,
@@ -102,24 +113,25 @@ class BobavikModel(BaseLM):
                  max_tokens: Optional[int] = None, stop_token_id: Optional[int] = None,
                  tensor_core_projections: bool = True, **_unused):
         if dtype not in (torch.bfloat16, torch.float32):
-            raise VoxB200Error(f"Bobavik runs in bfloat16 or float32, not {dtype}")
+            raise VoxB200Error(f"{self.design} runs in bfloat16 or float32, not {dtype}")
         super().__init__(model_name, device, dtype, enable_torch_compile, audio_decoder_device)
         if not torch.cuda.is_available():
-            raise VoxB200Error("BobavikModel needs a CUDA device: there is no CPU path")
+            raise VoxB200Error(f"{type(self).__name__} needs a CUDA device: there is no CPU path")
         if state_dict is None:
             if os.path.isdir(model_name):
                 with open(os.path.join(model_name, "config.json")) as f:
                     config = json.load(f)
                 state_dict = read_safetensors(os.path.join(model_name, "model.safetensors"))
-            elif model_name.startswith("bobavik-synthetic") and config is not None:
+            elif model_name.startswith(self.synthetic_name) and config is not None:
                 seed = int(model_name.split(":")[1]) if ":" in model_name else 0
-                state_dict = synthetic_state_dict(HybridConfig.from_json(config), seed, device)
+                cfg = self.read_config(config) if isinstance(config, dict) else config
+                state_dict = self.synthetic_weights(cfg, seed, device)
             else:
                 raise VoxB200Error(f"'{model_name}': pass a directory with config.json + model.safetensors, "
-                                   "state_dict= and config=, or 'bobavik-synthetic[:seed]' with config=")
+                                   f"state_dict= and config=, or '{self.synthetic_name}[:seed]' with config=")
         if config is None:
-            raise VoxB200Error("BobavikModel needs its configuration (config=)")
-        self.config = HybridConfig.from_json(config) if isinstance(config, dict) else config
+            raise VoxB200Error(f"{type(self).__name__} needs its configuration (config=)")
+        self.config = self.read_config(config) if isinstance(config, dict) else config
         self.weights = HybridWeights(state_dict, self.config, dtype, device, tensor_core=tensor_core_projections)
         self._max_tokens = max_tokens or 4096
         self.stop_token_id = -1 if stop_token_id is None else stop_token_id
@@ -135,7 +147,7 @@ class BobavikModel(BaseLM):
     output_audio_length = 0
 
     def _first_attention(self):
-        return next((L.mixer for L in self.config.layers if L.kind == "attention"), None)
+        return next((L.mixer for L in self.config.layers if L.kind in ("attention", "latent")), None)
 
     @property
     def num_attention_heads(self) -> int:
@@ -145,7 +157,7 @@ class BobavikModel(BaseLM):
     @property
     def num_key_value_heads(self) -> int:
         m = self._first_attention()
-        return m.kv_heads if m else 0
+        return getattr(m, "kv_heads", 1) if m else 0
 
     @property
     def num_hidden_layers(self) -> int:
@@ -168,6 +180,11 @@ class BobavikModel(BaseLM):
     def max_tokens(self) -> int:
         return self._max_tokens
 
+    @property
+    def max_positions(self) -> int:
+        """The longest sequence (prompt + generated) the design can address: the rows of a learned position table."""
+        return self.config.positions or (1 << 30)
+
     def is_stop_id(self, token_ids: List[int]) -> bool:
         return self.stop_token_id >= 0 and token_ids[0] == self.stop_token_id
 
@@ -189,6 +206,8 @@ class BobavikModel(BaseLM):
             raise VoxB200Error("empty prompt")
         if int(ids.min()) < 0 or int(ids.max()) >= self.config.vocab:
             raise VoxB200Error(f"token id outside [0, {self.config.vocab})")
+        if ids.numel() > self.max_positions:
+            raise VoxB200Error(f"prompt of {ids.numel()} tokens exceeds the model's {self.max_positions} positions")
         return PreprocessOutput(input_tokens=ids)
 
     def forward(self, step: StepInputs, engine: HybridEngine = None, **kwargs) -> torch.Tensor:
@@ -211,7 +230,7 @@ class BobavikModel(BaseLM):
         """The request-state coroutine of a step.  A request that is still in the middle of its prompt (or whose next token
         is given) takes no sampled token."""
         takes = [not r.pending_tokens for r in requests]
-        stop_id, max_tokens = self.stop_token_id, self.max_tokens
+        stop_id, max_tokens, max_pos = self.stop_token_id, self.max_tokens, self.max_positions
 
         async def update_req_states():
             if ids_host is not None:
@@ -233,6 +252,8 @@ class BobavikModel(BaseLM):
                 elif len(req.lm_output_tokens) >= (req.sampling_config.max_tokens if req.sampling_config and
                                                    req.sampling_config.max_tokens else max_tokens):
                     req.done_lm_generation, req.finish_reason = True, "max_tokens_reached"
+                elif (req.next_position_id or 0) >= max_pos:
+                    req.done_lm_generation, req.finish_reason = True, "max_positions_reached"
 
         return update_req_states()
 

@@ -440,10 +440,13 @@ def _packed(w, tile_rows: int) -> PackedWeight:
     return hit[0]
 
 
+GEMM_ACTS = {None: 0, "relu2": 1, "gelu": 2, "gelu_tanh": 3}
+
+
 def gemm(x, w, mode: int = 0, split_k: int = 1, out=None, tile_rows: int = 128, n_out: Optional[int] = None,
-         bias: Optional[torch.Tensor] = None):
+         bias: Optional[torch.Tensor] = None, act: Optional[str] = None):
     """x [T, K] bf16, w [N, K] bf16 (nn.Linear.weight layout, or a PackedWeight).  bias (bf16 [N], mode 0 only) is added
-    in fp32 before the single bf16 rounding.
+    in fp32 before the single bf16 rounding; act (mode 0 only: "relu2", "gelu", "gelu_tanh") applies to that fp32 value.
     mode 0 -> bf16 [T, N]; mode 1 -> fp32 partials [split_k, T, N]; mode 2 -> bf16 [T, n_out] = silu(gate)*up
     with w rows packed per tile_rows-row tile (see interleave_gate_up; n_out defaults to N/2)."""
     pw = _packed(w, tile_rows)
@@ -461,7 +464,7 @@ def gemm(x, w, mode: int = 0, split_k: int = 1, out=None, tile_rows: int = 128, 
     if isinstance(out, TiledAct):
         assert mode == 2 and out.T == T and out.K == n_out
         call("vb_gemm_bf16", out.data.data_ptr(), pw.data.data_ptr(), x_map_ptr, x_tiles_ptr, T, N, K, n_out, mode, split_k,
-             tile_rows, n_out, 1, None, _stream())
+             tile_rows, n_out, 1, None, 0, _stream())
         return out
     if out is None:
         if mode == 1:
@@ -471,8 +474,9 @@ def gemm(x, w, mode: int = 0, split_k: int = 1, out=None, tile_rows: int = 128, 
     if bias is not None:
         _need_cuda(bias)
         assert mode == 0 and bias.dtype == BF16 and bias.numel() == N and bias.is_contiguous()
+    assert act is None or mode == 0
     call("vb_gemm_bf16", out.data_ptr(), pw.data.data_ptr(), x_map_ptr, x_tiles_ptr, T, N, K, n_out, mode, split_k,
-         tile_rows, n_out, 0, _p(bias), _stream())
+         tile_rows, n_out, 0, _p(bias), GEMM_ACTS[act], _stream())
     return out
 
 
@@ -921,13 +925,63 @@ def _dt(x) -> int:
     raise VoxB200Error(f"dtype {d}: the hybrid kernels take bfloat16 or float32")
 
 
-def embed_rows_f32(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out [T, W] fp32 = table[ids] (table bf16 or fp32)."""
+def embed_rows_f32(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, pos_table: Optional[torch.Tensor] = None,
+                   pos: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out [T, W] fp32 = table[ids] (+ pos_table[pos]: learned positions); tables bf16 or fp32, of one type."""
     _need_cuda(table, ids, out)
     assert ids.dtype == torch.int32 and out.dtype == F32 and table.is_contiguous() and out.is_contiguous()
+    if pos_table is not None:
+        assert pos_table.dtype == table.dtype and pos_table.is_contiguous() and pos_table.shape[1] == table.shape[1]
+        assert pos.dtype == torch.int32 and pos.numel() >= ids.numel()
     call("vb_embed_rows_f32", out.data_ptr(), table.data_ptr(), ids.data_ptr(), ids.numel(), table.shape[1],
-         table.shape[0], _dt(table), _stream())
+         table.shape[0], _dt(table), _p(pos_table), _p(pos), pos_table.shape[0] if pos_table is not None else 0, _stream())
     return out
+
+
+def rmsnorm2_f32(x: torch.Tensor, w1: torch.Tensor, eps: float, out1: torch.Tensor, w2: Optional[torch.Tensor] = None,
+                 out2: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out1[t] = x[r] / sqrt(mean(x[r]^2) + eps) * w1 and, when given, out2[t] the same with w2 (r = rows[t] if rows is given
+    else t); x, w fp32; outputs bf16 or fp32, of one type."""
+    _need_cuda(x, w1, out1)
+    assert x.dtype == F32 and w1.dtype == F32 and x.is_contiguous() and out1.is_contiguous()
+    assert out2 is None or (out2.dtype == out1.dtype and out2.is_contiguous() and w2 is not None and w2.dtype == F32)
+    call("vb_rmsnorm2_f32", out1.data_ptr(), _p(out2), x.data_ptr(), w1.data_ptr(), _p(w2), _p(rows), out1.shape[0],
+         x.shape[1], float(eps), _dt(out1), _stream())
+    return out1
+
+
+def residual_side_f32(x: torch.Tensor, y1: torch.Tensor, y2: Optional[torch.Tensor], mult: float, eps: float,
+                      side: Optional[Tuple] = None, out1: Optional[torch.Tensor] = None, w1: Optional[torch.Tensor] = None,
+                      out2: Optional[torch.Tensor] = None, w2: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The tail of a block with parallel sublayers, in place on the fp32 stream x [T, W]: x += mult * (y1 + y2); with
+    side = (gate_w [d, W], proj_w [W, d], norm_w fp32 [W], table [vocab, ld], column offset, ids int32 [T]):
+    x += mult * rms_norm(proj_w (gelu_tanh(gate_w x) * table[ids][off : off + d])) * norm_w; then out1 / out2 = RMS norms of
+    the new x with w1 / w2 (bf16 or fp32)."""
+    _need_cuda(x, y1)
+    T, W = x.shape
+    assert x.dtype == F32 and y1.dtype == F32 and x.is_contiguous() and y1.is_contiguous() and tuple(y1.shape) == (T, W)
+    assert y2 is None or (y2.dtype == F32 and y2.is_contiguous() and tuple(y2.shape) == (T, W))
+    g = pj = nw = tb = ids = None
+    d = ld = off = vocab = wdt = 0
+    if side is not None:
+        g, pj, nw, tb, off, ids = side
+        d, ld, vocab, wdt = g.shape[0], tb.shape[1], tb.shape[0], _dt(g)
+        assert g.dtype == pj.dtype == tb.dtype and nw.dtype == F32 and ids.dtype == torch.int32
+        assert tuple(g.shape) == (d, W) and tuple(pj.shape) == (W, d) and g.is_contiguous() and pj.is_contiguous() and tb.is_contiguous()
+    assert out1 is None or (out1.is_contiguous() and w1.dtype == F32)
+    assert out2 is None or (out1 is not None and out2.dtype == out1.dtype and out2.is_contiguous() and w2.dtype == F32)
+    call("vb_residual_side_f32", x.data_ptr(), y1.data_ptr(), _p(y2), float(mult), _p(g), _p(pj), _p(nw), _p(tb), _p(ids), d, ld,
+         int(off), vocab, wdt, _p(out1), _p(w1), _p(out2), _p(w2), T, W, float(eps), _dt(out1) if out1 is not None else 1,
+         _stream())
+    return x
+
+
+def softcap_f32(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x = cap * tanh(x / cap) in place (fp32)."""
+    _need_cuda(x)
+    assert x.dtype == F32 and x.is_contiguous()
+    call("vb_softcap_f32", x.data_ptr(), x.numel(), float(cap), _stream())
+    return x
 
 
 def layernorm_f32(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, eps: float, out: torch.Tensor,
@@ -959,7 +1013,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 
            rows: Optional[int] = None) -> torch.Tensor:
     """out [R, N] = alpha * x @ w^T with fp32 accumulation.  x [T, K] and w ([N, K], or [E, N, K] with row_off
     [E + 1] for experts) share a dtype (bf16 or fp32); out bf16 or fp32.  epilogue 1: w holds N gate rows then N up rows
-    (per expert) and out = silu(gate) * up.  gather: int32 source row of x for every output row.  rows: how many rows a
+    (per expert) and out = silu(gate) * up; 2 / 3 / 4: out = relu(y)^2 / gelu(y) (erf) / gelu(y) (tanh form).  gather: int32 source row of x for every output row.  rows: how many rows a
     group can have at most (grouped) / how many rows to compute (dense); default x.shape[0]."""
     _need_cuda(x, w, out)
     assert x.dtype == w.dtype and x.stride(-1) == 1 and w.is_contiguous() and out.stride(-1) == 1
@@ -971,6 +1025,39 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 
     call("vb_linear", out.data_ptr(), x.data_ptr(), w.data_ptr(), T, N, K, x.stride(0), out.stride(0), _dt(x), _dt(out),
          epilogue, float(alpha), _p(row_off), _p(gather), groups, n_rows_w * K, _stream())
     return out
+
+
+LINEAR_ACTS = {None: 0, "relu2": 2, "gelu": 3, "gelu_tanh": 4}
+
+
+def linear_batched(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None,
+                   alpha: float = 1.0, epilogue: int = 0) -> torch.Tensor:
+    """out[t, g, :] = alpha * w[g] @ x[t, g, :] for every group g (the heads of a token side by side): x [T, G, K],
+    w [G, N, K] (one dtype, bf16 or fp32), out [T, G, N] (bf16 or fp32), fp32 accumulation in k order.  gate: an fp32 view
+    [T, >= G] (any row stride); out[t, g, :] is multiplied by sigmoid(gate[t, g])."""
+    _need_cuda(x, w, out)
+    T, G, K = x.shape
+    N = w.shape[1]
+    assert x.dtype == w.dtype and x.is_contiguous() and w.is_contiguous() and out.is_contiguous()
+    assert tuple(w.shape) == (G, N, K) and tuple(out.shape) == (T, G, N)
+    assert gate is None or (gate.dtype == F32 and gate.stride(1) == 1 and gate.shape[1] >= G)
+    call("vb_linear_batched", out.data_ptr(), x.data_ptr(), w.data_ptr(), T, N, K, G * K, G * N, K, N, N * K, G, _dt(x),
+         _dt(out), epilogue, float(alpha), _p(gate), gate.stride(0) if gate is not None else 0, _stream())
+    return out
+
+
+def latent_norm_append(proj: torch.Tensor, q_off: int, c_off: int, q_rank: int, kv_rank: int, wq: torch.Tensor,
+                       wc: Optional[torch.Tensor], cq_out: torch.Tensor, c_cache: Optional[torch.Tensor],
+                       row_req: torch.Tensor, pos: torch.Tensor, page_indptr: torch.Tensor, page_indices: torch.Tensor,
+                       T: int, eps: float) -> None:
+    """proj fp32 [T, ld]: the query latent at q_off is RMS-normed (wq) into cq_out [T, q_rank]; the key/value latent at
+    c_off is RMS-normed (wc) and appended to c_cache [pages, page, 1, kv_rank] (None: the layer reads another layer's)."""
+    _need_cuda(proj, cq_out)
+    assert proj.dtype == F32 and proj.stride(1) == 1 and wq.dtype == F32 and cq_out.is_contiguous()
+    assert c_cache is None or (c_cache.dtype == cq_out.dtype and c_cache.is_contiguous() and wc.dtype == F32)
+    call("vb_latent_norm_append", proj.data_ptr(), proj.stride(0), q_off, c_off, q_rank, kv_rank, wq.data_ptr(), _p(wc),
+         cq_out.data_ptr(), _p(c_cache), row_req.data_ptr(), pos.data_ptr(), page_indptr.data_ptr(), page_indices.data_ptr(),
+         c_cache.shape[1] if c_cache is not None else 1, T, float(eps), _dt(cq_out), _stream())
 
 
 def cast_f32_bf16(src: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -1087,6 +1174,21 @@ def moe_route(h: torch.Tensor, router_w: torch.Tensor, router_b: Optional[torch.
          h.shape[1], router_w.shape[0], top, _dt(h), _stream())
 
 
+def moe_route_sigmoid(h: torch.Tensor, router_w: torch.Tensor, correction: Optional[torch.Tensor], top: int,
+                      idx: torch.Tensor, wts: torch.Tensor, groups: int = 0, keep: int = 0,
+                      shared_gate_w: Optional[torch.Tensor] = None, shared_gate: Optional[torch.Tensor] = None) -> None:
+    """Scores sigmoid(router_w h) (fp32); the `top` experts with the largest score + correction, among the experts of the
+    `keep` best of `groups` groups of neighbours when groups > 1; weights = the chosen scores / (their sum + 1e-20).
+    idx int32 [T, top], wts fp32 [T, top].  shared_gate_w fp32 [W]: shared_gate[t] = sigmoid(shared_gate_w . h[t])."""
+    _need_cuda(h, router_w, idx, wts)
+    assert router_w.dtype == F32 and idx.dtype == torch.int32 and wts.dtype == F32 and h.is_contiguous()
+    assert correction is None or (correction.dtype == F32 and correction.numel() == router_w.shape[0])
+    assert shared_gate_w is None or (shared_gate_w.dtype == F32 and shared_gate_w.numel() == h.shape[1] and shared_gate.dtype == F32)
+    call("vb_moe_route_sigmoid", idx.data_ptr(), wts.data_ptr(), _p(shared_gate), h.data_ptr(), router_w.data_ptr(),
+         _p(correction), _p(shared_gate_w), h.shape[0], h.shape[1], router_w.shape[0], top, int(groups), int(keep), _dt(h),
+         _stream())
+
+
 def moe_group(idx: torch.Tensor, T: int, experts: int, top: int, row_off: torch.Tensor, sorted_token: torch.Tensor,
               pair_row: torch.Tensor, tile_rows: int = 0, tile_group: Optional[torch.Tensor] = None) -> None:
     """Counting sort of the (token, choice) pairs by expert.  tile_rows > 0: the padded layout for grouped tensor-core
@@ -1108,31 +1210,35 @@ def moe_gather_rows(x: torch.Tensor, token: torch.Tensor, out: torch.Tensor) -> 
 
 def gemm_grouped(x: torch.Tensor, w: "PackedWeight", out: torch.Tensor, mode: int, N: int, K: int, t_tile: int,
                  tile_group: Optional[torch.Tensor], group_bytes: int = 0, w_kb_stride: int = 0, group_kb: int = 0,
-                 kb_base: int = 0, n_out: Optional[int] = None) -> torch.Tensor:
+                 kb_base: int = 0, n_out: Optional[int] = None, act: Optional[str] = None) -> torch.Tensor:
     """Projection of row tiles (t_tile rows each) by the weights of their group inside one packed buffer (see vb_api.h):
-    N, K are one group's problem sizes.  mode 1 -> fp32 out [T, N]; mode 2 -> bf16 out [T, n_out] = silu(gate) * up."""
+    N, K are one group's problem sizes.  mode 0 -> bf16 out [T, N] after ``act``; mode 1 -> fp32 out [T, N]; mode 2 -> bf16
+    out [T, n_out] = silu(gate) * up."""
     _need_cuda(x, out)
     assert x.dtype == BF16 and x.dim() == 2 and x.shape[1] == K and out.is_contiguous()
     assert tile_group is None or x.shape[0] % t_tile == 0
     n_out = (N // 2 if mode == 2 else N) if n_out is None else n_out
     call("vb_gemm_bf16_grouped", out.data_ptr(), w.data.data_ptr(), tensor_map_2d(x, t_tile).ptr, x.shape[0], N, K, n_out,
          mode, w.tile_rows, n_out, t_tile, _p(tile_group), int(group_bytes), int(w_kb_stride), int(group_kb), int(kb_base),
-         _stream())
+         GEMM_ACTS[act], _stream())
     return out
 
 
 def moe_combine(expert_out: torch.Tensor, shared_out: Optional[torch.Tensor], wts: torch.Tensor, pair_row: torch.Tensor,
-                top: int, out: torch.Tensor) -> torch.Tensor:
+                top: int, out: torch.Tensor, shared_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """shared_scale fp32 [T]: the shared expert's output is multiplied by it per token."""
     assert expert_out.dtype == F32 and out.dtype == F32 and expert_out.is_contiguous() and out.is_contiguous()
     call("vb_moe_combine", out.data_ptr(), expert_out.data_ptr(), _p(shared_out), wts.data_ptr(), pair_row.data_ptr(),
-         out.shape[0], out.shape[1], top, _stream())
+         out.shape[0], out.shape[1], top, _p(shared_scale), _stream())
     return out
 
 
-def moe_scale_dense(act: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, experts: int, ff: int, top: int) -> torch.Tensor:
-    """act bf16 [T, >= experts * ff] in place: columns of expert e times the token's routing weight for e (0 if not chosen)."""
+def moe_scale_dense(act: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, experts: int, ff: int, top: int,
+                    shared_gate: Optional[torch.Tensor] = None, shared_ff: int = 0) -> torch.Tensor:
+    """act bf16 [T, >= experts * ff] in place: columns of expert e times the token's routing weight for e (0 if not chosen);
+    with shared_gate (fp32 [T]) the shared_ff columns after the experts' times the token's gate."""
     _need_cuda(act, idx, wts)
     assert act.dtype == BF16 and act.stride(1) == 1
     call("vb_moe_scale_dense", act.data_ptr(), idx.data_ptr(), wts.data_ptr(), act.shape[0], act.stride(0), experts, ff, top,
-         _stream())
+         _p(shared_gate), int(shared_ff), _stream())
     return act
