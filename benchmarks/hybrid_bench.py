@@ -4,6 +4,10 @@ uses (top * ff + shared ff).  Random weights, a few layers of a real model's sha
 
     python bench.py --arch bobavik [--arch-sizes 2048,3072] [--steps K] [--warmup W]
 
+``--arch razevik``: the Razevik design (latent attention, parallel blocks, sigmoid group router, side input) beside its
+closest relative on the same engine, Bobavik with softmax-attention layers only, at equal width, heads, head size and
+expert sizes.
+
 Per size and engine: prefill of one 1024-token prompt (eager launches) and one decode step of 32 requests at context 512
 (a CUDA-graph replay, as served), timed with CUDA events after warm-up; an L2-sized buffer is overwritten between timed
 iterations.  Output: one JSON line per size.
@@ -17,14 +21,32 @@ import torch
 PROMPT, BATCH, CONTEXT, LAYERS, VOCAB = 1024, 32, 512, 4, 32000
 
 
-def bobavik_config(width: int, ff: int, experts: int = 8, top: int = 2, window: int = 4096) -> dict:
+def razevik_config(width: int, ff: int, experts: int = 8, top: int = 2) -> dict:
+    """four blocks: own latents + dense feed-forward, then (shared, own, shared) with experts, as small models of the
+    design are laid out; 128-wide heads, a key/value latent of 128 dims, a query latent of 3/8 of the width"""
+    heads = width // 128
+    mix = {"heads": heads, "dim": 128, "vdim": 128, "kv_rank": 128, "q_rank": width * 3 // 8, "scale": 128 ** -0.5}
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top, "groups": {"count": 4, "keep": 2}}, "expert": {"ff": ff},
+           "shared": {"ff": ff}}
+    layers = []
+    for i in range(LAYERS):
+        m = dict(mix)
+        if i % 2:
+            m["kv_from"] = i - 1
+        layers.append({"type": "latent_attention", "mixer": m, "mlp": {"kind": "dense", "ff": 3 * ff} if i == 0 else dict(moe)})
+    return {"architecture": "Razevik", "width": width, "vocab": VOCAB, "max_positions": 2048, "norm": {"eps": 1e-6},
+            "residual_mult": 0.5, "token_side": {"dim": 32}, "logit_softcap": 30.0, "layers": layers}
+
+
+def bobavik_config(width: int, ff: int, experts: int = 8, top: int = 2, window: int = 4096,
+                   kinds=("attention", "lightning", "lightning", "attention")) -> dict:
     heads = width // 128
     att = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "v_mix": True,
            "mask": {"size": window}, "rot": {"dims": 64, "base": 1e6,
                                              "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
     lin = {"heads": heads, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** -(5 + 3 * h / heads) for h in range(heads)]}
     mlp = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff}, "shared": {"ff": ff}}
-    kinds = ["attention", "lightning", "lightning", "attention"]
+    kinds = list(kinds)
     return {"architecture": "Bobavik", "width": width, "vocab": VOCAB, "norm": {"eps": 1e-6}, "logit_scale": 1.0,
             "layers": [{"type": k, "mixer": dict(att if k == "attention" else lin), "mlp": dict(mlp)}
                        for k in (kinds * LAYERS)[:LAYERS]]}
@@ -58,13 +80,17 @@ def _graph(fn):
     return g.replay
 
 
-def bench_bobavik(width: int, ff: int, steps: int, warmup: int, flush) -> dict:
+def bench_bobavik(width: int, ff: int, steps: int, warmup: int, flush, kinds=None, design: str = "bobavik") -> dict:
     from vox_serve_b200 import ops
     from vox_serve_b200.hybrid_engine import StepInputs
     from vox_serve_b200.model.bobavik import BobavikModel
+    from vox_serve_b200.model.razevik import RazevikModel
 
-    cfg = bobavik_config(width, ff)
-    model = BobavikModel("bobavik-synthetic:1", config=cfg, device="cuda:0")
+    if design == "razevik":
+        model = RazevikModel("razevik-synthetic:1", config=razevik_config(width, ff), device="cuda:0")
+    else:
+        cfg = bobavik_config(width, ff, **({"kinds": kinds} if kinds else {}))
+        model = BobavikModel("bobavik-synthetic:1", config=cfg, device="cuda:0")
     page = 64
     pages_per_req = (CONTEXT + page) // page + 1
     n_pages = max(BATCH * pages_per_req, PROMPT // page + 1)
@@ -147,10 +173,21 @@ def bench_llama(width: int, inter: int, steps: int, warmup: int, flush) -> dict:
             "decode_tok_s": BATCH / t_dec * 1e3, "weight_gb": w.nbytes() / 1e9}
 
 
-def run(sizes, steps: int, warmup: int, only: str = "") -> None:
+def run(sizes, steps: int, warmup: int, only: str = "", arch: str = "bobavik") -> None:
     flush = torch.zeros(192 << 20, dtype=torch.uint8, device="cuda")
     for width in sizes:
         ff = width                     # expert width; a token uses top (2) experts + the shared one
+        if arch == "razevik":
+            line = {"bench": "razevik_vs_bobavik_attention", "width": width, "layers": LAYERS, "prompt": PROMPT,
+                    "decode_batch": BATCH, "context": CONTEXT, "steps": steps, "warmup": warmup, "dtype": "bf16",
+                    "data": "synthetic", "l2": "192 MiB buffer overwritten between timed iterations"}
+            if only in ("", "razevik"):
+                line["razevik"] = bench_bobavik(width, ff, steps, warmup, flush, design="razevik")
+            if only in ("", "bobavik"):
+                line["bobavik_attention"] = bench_bobavik(width, ff, steps, warmup, flush, kinds=("attention",) * LAYERS)
+            print(json.dumps(line), flush=True)
+            torch.cuda.empty_cache()
+            continue
         line = {"bench": "bobavik_vs_llama", "width": width, "layers": LAYERS, "prompt": PROMPT, "decode_batch": BATCH,
                 "context": CONTEXT, "steps": steps, "warmup": warmup, "dtype": "bf16", "data": "synthetic",
                 "l2": "192 MiB buffer overwritten between timed iterations"}

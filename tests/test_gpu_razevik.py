@@ -185,7 +185,7 @@ def test_other_sizes():
          {"kind": "own", "heads": 5, "dim": 4, "vdim": 10, "kv_rank": 24, "q_rank": 40, "scale": 0.5, "mlp": moe_b},
          {"kind": "bare", "heads": 2, "dim": 16, "vdim": 16, "kv_rank": 11, "q_rank": 9, "kv_from": 0, "mlp": moe_c},
          {"kind": "dense", "heads": 4, "dim": 6, "vdim": 5, "kv_rank": 13, "q_rank": 17}]
-    for width, side, cap, mult, dtype in ((52, 3, 0, 1.0, F32), (40, 0, 30.0, 0.35, F32), (52, 1, 4.0, 1.3, BF16)):
+    for width, side, cap, mult, dtype in ((52, 3, 0, 1.0, F32), (40, 0, 30.0, 0.35, F32), (52, 1, 12.0, 0.6, BF16)):
         cfg = O.make_config(width=width, vocab=37, layers=L, side_dim=side, softcap=cap, mult=mult, dense_ff=33)
         sd = O.random_weights(cfg, 7)
         toks = _tokens(40, 37, 1)
@@ -210,7 +210,7 @@ def test_prefill_decode_portions_and_batches(dtype):
     # token by token from the first token on
     assert _err(_replay(w, {"c": seqs["c"]}, [[("c", 1)]] * 40)["c"], ref["c"]) < TOL[dtype]
     # portions of changing size, down to two tokens, ending inside and at page borders
-    for cuts in ((2, 3, 11, 8, 16, 2, 33), (64, 2, 2, 7), (7, 1, 1, 8, 59)):
+    for cuts in ((2, 3, 11, 8, 16, 2, 33), (64, 2, 2, 7), (7, 1, 1, 8, 58)):
         assert sum(cuts) == 75
         got = _replay(w, {"a": seqs["a"]}, [[("a", n)] for n in cuts])["a"]
         assert _err(got, ref["a"]) < TOL[dtype], cuts
@@ -365,7 +365,7 @@ def test_norms_side_input_and_batched_projection():
         ref = O.token_side(x.double() + 0.6 * (y1 + y2).double(), ids, 1, sdw, cfg)
         xd = x.to(DEV).clone()
         o1, o2 = torch.zeros(T, W, dtype=F32, device=DEV), torch.zeros(T, W, dtype=F32, device=DEV)
-        side = (sdw["l1.side.gate"].to(DEV), sdw["l1.side.proj"].to(DEV), sd["l1.side.norm"].to(DEV), sdw["side.embed"].to(DEV),
+        side = (sdw["l1.side.gate"].to(DEV), sdw["l1.side.proj"].to(DEV), sdw["l1.side.norm"].float().to(DEV), sdw["side.embed"].to(DEV),
                 d, ids.to(DEV, I32))
         ops.residual_side_f32(xd, y1.to(DEV), y2.to(DEV), 0.6, 1e-4, side, o1, w1.to(DEV), o2, w2.to(DEV))
         assert torch.allclose(xd.cpu().double(), ref, rtol=2e-5, atol=2e-5)
