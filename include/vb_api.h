@@ -531,6 +531,9 @@ int vb_sum_planes_f32(float* d_out, const float* d_partials, int planes, long lo
  *                       sigmoid(gate[t][h]) if gate; window <= 0 = no window.  d_part (optional, part_floats fp32): scratch
  *                       that lets steps of few rows split a row's keys over several CTAs.  d_row_list (optional): the T
  *                       rows to serve (steps that run their prompt portions on the tiled kernel and the rest here).
+ *                       head_rows: bf16 heads of tensor-core sizes with 2 .. 64 query heads per key/value head run as
+ *                       tensor-core tiles whose rows are those heads (K / V tiles staged once per group); other cases
+ *                       ignore the flag.  Key and value caches that are ONE tensor of equal head sizes are staged once.
  * vb_window_attn_tiled: the same result for prompt portions: tile i covers rows tile_row0[i].. (at most
  *                       vb_window_attn_tile_rows()) of request tile_req[i], whose rows are consecutive positions */
 int vb_rotary_table(float* d_cs, const int32_t* d_pos, const double* d_freq, int T, int half, void* stream);
@@ -550,7 +553,8 @@ int vb_latent_norm_append(const float* d_proj, int ldp, int q_off, int c_off, in
 int vb_window_attn(void* d_out, const void* d_q, const void* d_k_cache, const void* d_v_cache, const float* d_gate,
                    int ld_gate, const int32_t* d_row_req, const int32_t* d_pos, const int32_t* d_page_indptr,
                    const int32_t* d_page_indices, int T, int H, int G, int dim, int vdim, int page_size, int window,
-                   float scale, int dtype, float* d_part, long long part_floats, const int32_t* d_row_list, void* stream);
+                   float scale, int dtype, float* d_part, long long part_floats, const int32_t* d_row_list, int head_rows,
+                   void* stream);
 int vb_window_attn_tile_rows(void);
 int vb_window_attn_tiled(void* d_out, const void* d_q, const void* d_k_cache, const void* d_v_cache, const float* d_gate,
                          int ld_gate, const int32_t* d_pos, const int32_t* d_page_indptr, const int32_t* d_page_indices,

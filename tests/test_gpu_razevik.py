@@ -300,13 +300,13 @@ def _latent_case(n_tokens, page_size, hot, dtype, tiled, H=3, D=8, V=4, R=16):
     q_lat = ops.linear_batched(q.to(DEV, dtype).contiguous(), uk_t, torch.zeros(T, H, R, dtype=dtype, device=DEV))
     o_lat = torch.zeros(T, H * R, dtype=dtype, device=DEV)
     tiles = None
-    if tiled:
+    if tiled is True:
         rows = ops.window_attn_tile_rows()
         r0 = torch.arange(0, T, rows, dtype=I32, device=DEV)
         tiles = (torch.tensor([0, T], dtype=I32, device=DEV), torch.zeros_like(r0), r0, r0.numel())
     scratch = torch.full((T * H * 8 * (R + 2),), float("nan"), dtype=F32, device=DEV)
     ops.window_attn(q_lat.view(T, H * R), cache, cache, o_lat, None, row_req, pos, indptr, perm.to(DEV), T, H, 1, R, R, 0, 1.0,
-                    tiles=tiles, scratch=scratch)
+                    tiles=tiles, scratch=scratch if T < 100 else None, head_rows=tiled == "heads")
     out = ops.linear_batched(o_lat.view(T, H, R), uv.view(H, V, R).to(DEV, dtype).contiguous(),
                              torch.zeros(T, H, V, dtype=dtype, device=DEV))
     # the plain form: keys and values of every head, position by position
@@ -321,11 +321,13 @@ def _latent_case(n_tokens, page_size, hot, dtype, tiled, H=3, D=8, V=4, R=16):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("tiled", [False, True])
+@pytest.mark.parametrize("tiled", [False, True, "heads"])
 @pytest.mark.parametrize("dtype", [F32, BF16])
 def test_latent_attention_far_keys_and_page_borders(tiled, dtype):
     """the hot latent is seen from its own position on, hundreds of positions and many pages away, and by no earlier query;
-    hot positions at the first token, the last slot of a page and the first slot of the next."""
+    hot positions at the first token, the last slot of a page and the first slot of the next.  tiled: prompt tiles; "heads":
+    every row on its own with its heads as the rows of a tensor-core tile (what single-token steps run in bfloat16), its keys
+    dealt to several CTAs in the shorter cases."""
     tol = 2e-3 if dtype == F32 else 4e-2
     sizes = dict(H=3, D=8, V=4, R=16) if dtype == F32 else dict(H=2, D=16, V=16, R=32)
     for hot, T, ps in ((0, 40, 8), (7, 300, 8), (8, 130, 8), (63, 200, 64), (64, 131, 64), (5, 70, 16)):
@@ -379,6 +381,14 @@ def test_norms_side_input_and_batched_projection():
     ref = torch.einsum("tgk,gnk->tgn", xb.double(), wb.double()) * torch.sigmoid(gate[:, :G].double())[:, :, None] * 0.5
     out = ops.linear_batched(xb.to(DEV), wb.to(DEV), torch.zeros(T, G, N, device=DEV), gate=gate.to(DEV)[:, :G], alpha=0.5)
     assert torch.allclose(out.cpu().double(), ref, rtol=1e-5, atol=1e-5)
+    # the same on tensor-core tiles (bfloat16, K a multiple of 16 that is none of 32, a partial last column tile, two row tiles)
+    T2, K, N = 70, 48, 72
+    xb, wb, gate = torch.randn(T2, G, K, generator=g).to(BF16), torch.randn(G, N, K, generator=g).to(BF16), torch.randn(T2, G, generator=g)
+    ref = torch.einsum("tgk,gnk->tgn", xb.double(), wb.double()) * torch.sigmoid(gate.double())[:, :, None] * 0.5
+    out = ops.linear_batched(xb.to(DEV), wb.to(DEV), torch.zeros(T2, G, N, dtype=BF16, device=DEV), gate=gate.to(DEV), alpha=0.5)
+    assert torch.allclose(out.cpu().double(), ref, rtol=1e-2, atol=2e-2)
+    out = ops.linear_batched(xb.to(DEV), wb.to(DEV), torch.zeros(T2, G, N, dtype=BF16, device=DEV))
+    assert torch.allclose(out.cpu().double(), torch.einsum("tgk,gnk->tgn", xb.double(), wb.double()), rtol=1e-2, atol=3e-2)
     # soft cap
     z = torch.randn(5, 9, generator=g) * 20
     assert torch.allclose(ops.softcap_f32(z.to(DEV).clone(), 7.0).cpu(), 7.0 * torch.tanh(z / 7.0), rtol=1e-5, atol=1e-5)

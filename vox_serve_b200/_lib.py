@@ -123,7 +123,7 @@ SIGNATURES = {
     "vb_qkv_rotary_append": (c_int, [P, c_int, c_int, c_int, c_int, P, c_int, P, P, P, P, P, P, P, c_int, c_int, c_int,
                                      c_int, c_int, c_int, c_int, P, P, c_int, P]),
     "vb_window_attn": (c_int, [P, P, P, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                               c_int, P, C.c_longlong, P, P]),
+                               c_int, P, C.c_longlong, P, c_int, P]),
     "vb_window_attn_tile_rows": (c_int, []),
     "vb_window_attn_tiled": (c_int, [P, P, P, P, P, c_int, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
                                      c_int, c_int, c_float, c_int, P]),

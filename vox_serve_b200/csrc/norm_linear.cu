@@ -103,67 +103,144 @@ struct ResidualSideParams {
   void* out2;
   const float* w1;
   const float* w2;
-  int W, side_dim, ld_e, e_off, vocab;
+  int W, side_dim, ld_e, e_off, vocab, T;
   float mult, eps;
 };
 
-template <typename WT, typename OT>
+// eight consecutive elements as fp32 (16-byte loads; the caller guarantees the alignment)
+template <typename WT> __device__ __forceinline__ void load8(const WT* __restrict__ p, float (&v)[8]);
+template <> __device__ __forceinline__ void load8<float>(const float* __restrict__ p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* __restrict__ p, float (&v)[8]) {
+  const uint4 a = *reinterpret_cast<const uint4*>(p);
+  v[0] = bf16_lo(a.x); v[1] = bf16_hi(a.x); v[2] = bf16_lo(a.y); v[3] = bf16_hi(a.y);
+  v[4] = bf16_lo(a.z); v[5] = bf16_hi(a.z); v[6] = bf16_lo(a.w); v[7] = bf16_hi(a.w);
+}
+
+// ROWS rows per CTA: the side matrices are read once per CTA and serve all of its rows (long steps), every row's sums
+// are formed in the same order whatever ROWS is, so a row's result does not depend on the step it is part of.
+template <typename WT, typename OT, int ROWS>
 __global__ void __launch_bounds__(256) residual_side_kernel(ResidualSideParams p) {
   extern __shared__ float sm[];
   const int W = p.W, SD = p.side_dim;
-  float* row = sm;              // [W]
-  float* yb = sm + W;           // [W]
-  float* g = yb + W;            // [SD]
-  float* red = g + SD;          // [64]
+  float* row = sm;                      // [ROWS][W]
+  float* yb = row + ROWS * W;           // [ROWS][W]
+  float* g = yb + ROWS * W;             // [ROWS][SD]
+  float* red = g + ROWS * SD;           // [64]
   int phase = 0;
   pdl_sync();
-  const size_t t = blockIdx.x;
+  const size_t t0 = static_cast<size_t>(blockIdx.x) * ROWS;
+  const int nr = min(ROWS, p.T - static_cast<int>(t0));
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    float y = p.y1[t * W + i];
-    if (p.y2) y += p.y2[t * W + i];
-    row[i] = fmaf(p.mult, y, p.x[t * W + i]);
-  }
+  for (int r = 0; r < nr; ++r)
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      float y = p.y1[(t0 + r) * W + i];
+      if (p.y2) y += p.y2[(t0 + r) * W + i];
+      row[r * W + i] = fmaf(p.mult, y, p.x[(t0 + r) * W + i]);
+    }
+  for (int r = nr; r < ROWS; ++r)
+    for (int i = threadIdx.x; i < W; i += blockDim.x) row[r * W + i] = 0.f;
   __syncthreads();
   if (p.side_gate) {
     const WT* Wg = static_cast<const WT*>(p.side_gate);
     const WT* Wp = static_cast<const WT*>(p.side_proj);
-    const int id = min(max(p.ids[t], 0), p.vocab - 1);
-    const WT* e = static_cast<const WT*>(p.side_embed) + static_cast<size_t>(id) * p.ld_e + p.e_off;
+    const bool vec = (W & 7) == 0 && (SD & 7) == 0;
     for (int d = warp; d < SD; d += nw) {
       const WT* wr = Wg + static_cast<size_t>(d) * W;
-      float s = 0.f;
-      for (int i = lane; i < W; i += 32) s = fmaf(to_f(wr[i]), row[i], s);
-      s = warp_sum(s);
-      if (lane == 0) g[d] = act_apply(s, 4) * to_f(e[d]);
+      float s[ROWS];
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) s[r] = 0.f;
+      if (vec) {
+        for (int i = lane * 8; i < W; i += 256) {
+          float wv[8];
+          load8<WT>(wr + i, wv);
+#pragma unroll
+          for (int r = 0; r < ROWS; ++r) {
+            const float4 a = *reinterpret_cast<const float4*>(row + r * W + i), b = *reinterpret_cast<const float4*>(row + r * W + i + 4);
+            float acc = s[r];
+            acc = fmaf(wv[0], a.x, acc); acc = fmaf(wv[1], a.y, acc); acc = fmaf(wv[2], a.z, acc); acc = fmaf(wv[3], a.w, acc);
+            acc = fmaf(wv[4], b.x, acc); acc = fmaf(wv[5], b.y, acc); acc = fmaf(wv[6], b.z, acc); acc = fmaf(wv[7], b.w, acc);
+            s[r] = acc;
+          }
+        }
+      } else {
+        for (int i = lane; i < W; i += 32) {
+          const float wv = to_f(wr[i]);
+#pragma unroll
+          for (int r = 0; r < ROWS; ++r) s[r] = fmaf(wv, row[r * W + i], s[r]);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        const float tot = warp_sum(s[r]);
+        if (lane == 0 && r < nr) {
+          const int id = min(max(p.ids[t0 + r], 0), p.vocab - 1);
+          const WT* e = static_cast<const WT*>(p.side_embed) + static_cast<size_t>(id) * p.ld_e + p.e_off;
+          g[r * SD + d] = act_apply(tot, 4) * to_f(e[d]);
+        }
+      }
     }
+    for (int i = threadIdx.x; i < (ROWS - nr) * SD; i += blockDim.x) g[nr * SD + i] = 0.f;
     __syncthreads();
-    float q = 0.f;
+    float q[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) q[r] = 0.f;
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
       const WT* wr = Wp + static_cast<size_t>(i) * SD;
-      float s = 0.f;
-      for (int d = 0; d < SD; ++d) s = fmaf(to_f(wr[d]), g[d], s);
-      yb[i] = s;
-      q = fmaf(s, s, q);
+      float s[ROWS];
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) s[r] = 0.f;
+      if (vec) {
+        for (int d = 0; d < SD; d += 8) {
+          float wv[8];
+          load8<WT>(wr + d, wv);
+#pragma unroll
+          for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) s[r] = fmaf(wv[e], g[r * SD + d + e], s[r]);
+        }
+      } else {
+        for (int d = 0; d < SD; ++d) {
+          const float wv = to_f(wr[d]);
+#pragma unroll
+          for (int r = 0; r < ROWS; ++r) s[r] = fmaf(wv, g[r * SD + d], s[r]);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        yb[r * W + i] = s[r];
+        q[r] = fmaf(s[r], s[r], q[r]);
+      }
     }
-    const float rs = 1.f / sqrtf(block_sum(q, red, phase) / W + p.eps);
-    for (int i = threadIdx.x; i < W; i += blockDim.x) row[i] = fmaf(p.mult, yb[i] * rs * p.side_norm[i], row[i]);
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const float rs = 1.f / sqrtf(block_sum(q[r], red, phase) / W + p.eps);
+      for (int i = threadIdx.x; i < W; i += blockDim.x)
+        row[r * W + i] = fmaf(p.mult, yb[r * W + i] * rs * p.side_norm[i], row[r * W + i]);
+    }
     __syncthreads();
   }
-  float q = 0.f;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    const float v = row[i];
-    p.x[t * W + i] = v;
-    q = fmaf(v, v, q);
-  }
-  if (p.out1 == nullptr) return;
-  const float rs = 1.f / sqrtf(block_sum(q, red, phase) / W + p.eps);
   OT* o1 = static_cast<OT*>(p.out1);
   OT* o2 = static_cast<OT*>(p.out2);
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    const float v = row[i] * rs;
-    o1[t * W + i] = from_f<OT>(v * p.w1[i]);
-    if (o2) o2[t * W + i] = from_f<OT>(v * p.w2[i]);
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+    float q = 0.f;
+    if (r < nr)
+      for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        const float v = row[r * W + i];
+        p.x[(t0 + r) * W + i] = v;
+        q = fmaf(v, v, q);
+      }
+    if (p.out1 == nullptr) continue;
+    const float rs = 1.f / sqrtf(block_sum(q, red, phase) / W + p.eps);
+    if (r < nr)
+      for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        const float v = row[r * W + i] * rs;
+        o1[(t0 + r) * W + i] = from_f<OT>(v * p.w1[i]);
+        if (o2) o2[(t0 + r) * W + i] = from_f<OT>(v * p.w2[i]);
+      }
   }
 }
 
@@ -354,6 +431,68 @@ __global__ void __launch_bounds__(256) linear_kernel(LinearParams p) {
   }
 }
 
+// The batched form on the tensor cores (bf16 in and out, K a multiple of 16, N a multiple of 8): CTA = 64 rows x 64
+// columns of one group, 4 warps x 16 rows, mma.sync m16n8k16 with fp32 accumulators over K chunks of 32 staged in shared
+// memory with 16-byte loads.  Every output is one accumulator fed in k order: a row's result does not depend on the rows
+// that share the launch.
+constexpr int BM_M = 64, BM_N = 64, BM_K = 32, BM_LD = BM_K + 8;
+
+__global__ void __launch_bounds__(128) linear_batched_mma_kernel(LinearParams p) {
+  __shared__ __align__(16) __nv_bfloat16 As[BM_M * BM_LD];
+  __shared__ __align__(16) __nv_bfloat16 Bs[BM_N * BM_LD];
+  pdl_sync();
+  const int z = blockIdx.z, m0 = blockIdx.x * BM_M, n0 = blockIdx.y * BM_N;
+  const __nv_bfloat16* X = static_cast<const __nv_bfloat16*>(p.x) + static_cast<size_t>(z) * p.x_group_stride;
+  const __nv_bfloat16* Wm = static_cast<const __nv_bfloat16*>(p.w) + static_cast<size_t>(z) * p.w_group_stride;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  float acc[BM_N / 8][4];
+#pragma unroll
+  for (int n = 0; n < BM_N / 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+  for (int k0 = 0; k0 < p.K; k0 += BM_K) {
+    // 64 rows x 4 pieces of 8 elements for each operand; pieces past K (K % 32 == 16) and rows past the edge are zero
+#pragma unroll
+    for (int i = tid; i < BM_M * 4; i += 128) {
+      const int r = i >> 2, c = (i & 3) * 8;
+      uint4 a = make_uint4(0u, 0u, 0u, 0u), b = a;
+      if (k0 + c < p.K) {
+        if (m0 + r < p.T) a = *reinterpret_cast<const uint4*>(X + static_cast<size_t>(m0 + r) * p.ldx + k0 + c);
+        if (n0 + r < p.N) b = *reinterpret_cast<const uint4*>(Wm + static_cast<size_t>(n0 + r) * p.K + k0 + c);
+      }
+      *reinterpret_cast<uint4*>(As + r * BM_LD + c) = a;
+      *reinterpret_cast<uint4*>(Bs + r * BM_LD + c) = b;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kb = 0; kb < BM_K / 16; ++kb) {
+      uint32_t af[4];
+      ldmatrix_x4(af, smem_u32(As + (warp * 16 + (lane & 15)) * BM_LD + kb * 16 + (lane >> 4) * 8));
+#pragma unroll
+      for (int np = 0; np < BM_N / 16; ++np) {
+        uint32_t bf[4];
+        ldmatrix_x4(bf, smem_u32(Bs + (np * 16 + (lane >> 4) * 8 + (lane & 7)) * BM_LD + kb * 16 + ((lane >> 3) & 1) * 8));
+        mma_bf16_16816(acc[2 * np], af, bf[0], bf[1]);
+        mma_bf16_16816(acc[2 * np + 1], af, bf[2], bf[3]);
+      }
+    }
+    __syncthreads();
+  }
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(z) * p.o_group_stride;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = m0 + warp * 16 + (lane >> 2) + 8 * half;
+    if (r >= p.T) continue;
+    float gmul = p.alpha;
+    if (p.gate) gmul *= 1.f / (1.f + expf(-p.gate[static_cast<size_t>(r) * p.ld_gate + z]));
+#pragma unroll
+    for (int n = 0; n < BM_N / 8; ++n) {
+      const int c = n0 + n * 8 + (lane & 3) * 2;
+      if (c < p.N)
+        *reinterpret_cast<uint32_t*>(out + static_cast<size_t>(r) * p.ldo + c) =
+            pack_bf16(acc[n][2 * half] * gmul, acc[n][2 * half + 1] * gmul);
+    }
+  }
+}
+
 template <typename XT, typename WT, typename OT>
 static int launch_linear(const LinearParams& p, int groups, int max_rows, cudaStream_t stream) {
   dim3 grid((max_rows + LB_M - 1) / LB_M, (p.N + LB_N - 1) / LB_N, groups);
@@ -425,9 +564,19 @@ int vb_rmsnorm2_f32(void* d_out1, void* d_out2, const float* d_x, const float* d
 }  // extern "C"
 
 template <typename WT, typename OT>
-static int launch_residual_side(const ResidualSideParams& p, int T, size_t smem, cudaStream_t stream) {
-  if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(residual_side_kernel<WT, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
-  VB_LAUNCH_PDL((residual_side_kernel<WT, OT>), T, 256, smem, stream, p);
+static int launch_residual_side(const ResidualSideParams& p, int T, cudaStream_t stream) {
+  // long steps: four rows per CTA share one pass over the side matrices (when that fits shared memory)
+  const size_t per_row = (2 * static_cast<size_t>(p.W) + p.side_dim) * sizeof(float);
+  const bool four = p.side_gate && T >= 256 && 4 * per_row + 256 <= static_cast<size_t>(VB_MAX_DYN_SMEM);
+  const size_t smem = (four ? 4 : 1) * per_row + 64 * sizeof(float);
+  VB_CHECK_ARG(smem <= static_cast<size_t>(VB_MAX_DYN_SMEM), "vb_residual_side_f32: width %d too large", p.W);
+  if (four) {
+    VB_CHECK_CUDA(cudaFuncSetAttribute(residual_side_kernel<WT, OT, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+    VB_LAUNCH_PDL((residual_side_kernel<WT, OT, 4>), (T + 3) / 4, 256, smem, stream, p);
+  } else {
+    if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(residual_side_kernel<WT, OT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+    VB_LAUNCH_PDL((residual_side_kernel<WT, OT, 1>), T, 256, smem, stream, p);
+  }
   return 0;
 }
 
@@ -444,13 +593,11 @@ int vb_residual_side_f32(float* d_x, const float* d_y1, const float* d_y2, float
   VB_CHECK_ARG((!d_out1 || d_w1) && (!d_out2 || (d_out1 && d_w2)), "vb_residual_side_f32: norms need weights");
   if (T <= 0) return 0;
   const int sd = d_side_gate ? side_dim : 0;
-  const size_t smem = (2 * static_cast<size_t>(width) + sd + 64) * sizeof(float);
-  VB_CHECK_ARG(smem <= static_cast<size_t>(VB_MAX_DYN_SMEM), "vb_residual_side_f32: width %d too large", width);
   ResidualSideParams p{d_x, d_y1, d_y2, d_side_gate, d_side_proj, d_side_norm, d_side_embed, d_ids, d_out1, d_out2, d_w1, d_w2,
-                       width, sd, ld_e, e_off, vocab, mult, eps};
+                       width, sd, ld_e, e_off, vocab, T, mult, eps};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (w_dtype == 1) return out_dtype == 1 ? launch_residual_side<float, float>(p, T, smem, s) : launch_residual_side<float, bf16>(p, T, smem, s);
-  return out_dtype == 1 ? launch_residual_side<bf16, float>(p, T, smem, s) : launch_residual_side<bf16, bf16>(p, T, smem, s);
+  if (w_dtype == 1) return out_dtype == 1 ? launch_residual_side<float, float>(p, T, s) : launch_residual_side<float, bf16>(p, T, s);
+  return out_dtype == 1 ? launch_residual_side<bf16, float>(p, T, s) : launch_residual_side<bf16, bf16>(p, T, s);
 }
 
 int vb_softcap_f32(float* d_x, long long n, float cap, void* stream) {
@@ -470,6 +617,14 @@ int vb_linear_batched(void* d_out, const void* d_x, const void* d_w, int T, int 
   LinearParams p{d_out, d_x, d_w, nullptr, nullptr, T, N, K, ldx, ldo, epilogue, w_group_stride, alpha, x_group_stride,
                  o_group_stride, d_gate, ld_gate, 1};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool aligned = ldx % 8 == 0 && x_group_stride % 8 == 0 && w_group_stride % 8 == 0 && ldo % 2 == 0 && o_group_stride % 2 == 0 &&
+                       reinterpret_cast<uintptr_t>(d_x) % 16 == 0 && reinterpret_cast<uintptr_t>(d_w) % 16 == 0 &&
+                       reinterpret_cast<uintptr_t>(d_out) % 4 == 0;
+  if (in_dtype == 0 && out_dtype == 0 && epilogue == 0 && K % 16 == 0 && N % 8 == 0 && aligned) {
+    dim3 grid((T + BM_M - 1) / BM_M, (N + BM_N - 1) / BM_N, groups);
+    VB_LAUNCH_PDL(linear_batched_mma_kernel, grid, 128, 0, stream, p);
+    return 0;
+  }
   if (in_dtype == 1) return out_dtype == 1 ? launch_linear<float, float, float>(p, groups, T, s) : launch_linear<float, float, bf16>(p, groups, T, s);
   return out_dtype == 1 ? launch_linear<bf16, bf16, float>(p, groups, T, s) : launch_linear<bf16, bf16, bf16>(p, groups, T, s);
 }

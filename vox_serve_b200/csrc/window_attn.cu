@@ -164,6 +164,8 @@ struct WindowAttnParams {
   int T, H, G, dim, vdim, page_size, window;   // window <= 0: every earlier position is visible
   float scale;
   const int32_t* row_list;    // per-row kernels: the rows to serve (nullptr: rows 0 .. T - 1); T counts the served rows
+  int row_heads;              // tensor-core tile kernel on single-token rows: a tile's rows are the query heads of ONE token
+                              // that share a key/value head (grid: served rows x key/value heads x splits)
   int splits;                 // grouped kernel: key tiles are dealt round-robin to `splits` CTAs per (row, key/value head)
   float* part;                // [T][H][splits][vdim + 2]: unnormalised output, running max, running sum of every split
 };
@@ -552,21 +554,33 @@ constexpr int FM = 64, FN = 64, F_KB = 8, F_NT = 16;      // dim <= 16 * F_KB, v
 __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnParams p) {
   extern __shared__ __align__(16) uint8_t smraw[];
   pdl_sync();
-  // later tiles of a prompt see more keys: they are started first so that the short ones fill the tail
-  const int tile = gridDim.x - 1 - blockIdx.x;
-  const int b = p.tile_req[tile], row0 = p.tile_row0[tile], h = blockIdx.y;
-  const int nrows = min(row0 + FM, p.qo_indptr[b + 1]) - row0;
+  // prompt portions: tile = 64 consecutive rows (positions) of one request and one query head.  Single-token rows
+  // (row_heads): tile = the R query heads of ONE token that share key/value head g, all at the token's position; the
+  // token's key tiles may be dealt to several CTAs (splits), whose shares vb::window_attn_merge_kernel puts together.
+  int b, row0, h, nrows, HH, pstep, pos0, g, S = 1, sidx = 0;
+  if (p.row_heads) {
+    const int t = p.row_list ? p.row_list[blockIdx.x] : blockIdx.x, R = p.H / p.G;
+    b = p.row_req[t]; g = blockIdx.y; row0 = t * p.H + g * R; h = 0; nrows = R; HH = 1; pstep = 0; pos0 = p.pos[t];
+    S = p.splits; sidx = blockIdx.z;
+  } else {
+    // later tiles of a prompt see more keys: they are started first so that the short ones fill the tail
+    const int tile = gridDim.x - 1 - blockIdx.x;
+    b = p.tile_req[tile]; row0 = p.tile_row0[tile]; h = blockIdx.y;
+    nrows = min(row0 + FM, p.qo_indptr[b + 1]) - row0;
+    HH = p.H; pstep = 1; pos0 = p.pos[row0]; g = h / (p.H / p.G);
+  }
+  // keys and values that are one tensor of equal head sizes (latent attention) are staged once and read as both
+  const bool same_kv = p.k_cache == p.v_cache && p.dim == p.vdim;
   const int dk = p.dim, dv = p.vdim, ldk = dk + 8, ldv = dv + 8, nkb = dk / 16, nvp = dv / 16;
   // two stages of K [64][dk + 8] | V [64][dv + 8]; the first stage's K region holds the Q tile first
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smraw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int g = h / (p.H / p.G);
   const __nv_bfloat16* q = static_cast<const __nv_bfloat16*>(p.q);
   const int qv = dk / 8;
   for (int i = tid; i < FM * qv; i += 128) {
     const int r = i / qv, c = (i - r * qv) * 8;
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (r < nrows) v = *reinterpret_cast<const uint4*>(q + (static_cast<size_t>(row0 + r) * p.H + h) * dk + c);
+    if (r < nrows) v = *reinterpret_cast<const uint4*>(q + (static_cast<size_t>(row0 + r) * HH + h) * dk + c);
     *reinterpret_cast<uint4*>(Ks + r * ldk + c) = v;
   }
   __syncthreads();
@@ -574,9 +588,9 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnParams p
 #pragma unroll
   for (int kb = 0; kb < F_KB; ++kb)
     if (kb < nkb) ldmatrix_x4(qf[kb], smem_u32(Ks + (warp * 16 + (lane & 15)) * ldk + kb * 16 + (lane >> 4) * 8));
-  const int pos0 = p.pos[row0], pos_last = pos0 + nrows - 1;
+  const int pos_last = pos0 + (nrows - 1) * pstep;
   const int rA = warp * 16 + (lane >> 2), rB = rA + 8;
-  const int posA = pos0 + rA, posB = pos0 + rB;
+  const int posA = pos0 + rA * pstep, posB = pos0 + rB * pstep;
   const bool okA = rA < nrows, okB = rB < nrows;
   const int loA = p.window > 0 ? max(0, posA - p.window + 1) : 0, loB = p.window > 0 ? max(0, posB - p.window + 1) : 0;
   const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
@@ -608,27 +622,29 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnParams p
       for (int c = piece; c < qv; c += 16)
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(Kd + kk * ldk + c * 8)),
                      "l"(kc + tok * dk + c * 8), "r"(nbytes) : "memory");
-      for (int c = piece; c < vv; c += 16)
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(Vd + kk * ldv + c * 8)),
-                     "l"(vc + tok * dv + c * 8), "r"(nbytes) : "memory");
+      if (!same_kv)
+        for (int c = piece; c < vv; c += 16)
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(Vd + kk * ldv + c * 8)),
+                       "l"(vc + tok * dv + c * 8), "r"(nbytes) : "memory");
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
   __syncthreads();                    // every warp holds its Q fragments: the first stage may be overwritten
-  issue_tile(lo, 0);
+  const int c_first = lo + sidx * FN, c_step = FN * S;
+  if (c_first <= pos_last) issue_tile(c_first, 0);
   int stage = 0;
-  for (int c0 = lo; c0 <= pos_last; c0 += FN, stage ^= 1) {
-    if (c0 + FN <= pos_last) {
-      issue_tile(c0 + FN, stage ^ 1);
+  for (int c0 = c_first; c0 <= pos_last; c0 += c_step, stage ^= 1) {
+    if (c0 + c_step <= pos_last) {
+      issue_tile(c0 + c_step, stage ^ 1);
       asm volatile("cp.async.wait_group 1;" ::: "memory");
     } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
     const __nv_bfloat16* Kt = Ks + stage * stage_elems;
-    const __nv_bfloat16* Vt = Kt + FN * ldk;
+    const __nv_bfloat16* Vt = same_kv ? Kt : Kt + FN * ldk;
     // a warp whose 16 rows see nothing of this tile has no work in it
-    const int w_first = pos0 + warp * 16, w_last = min(pos0 + warp * 16 + 15, pos_last);
+    const int w_first = pos0 + warp * 16 * pstep, w_last = min(pos0 + (warp * 16 + 15) * pstep, pos_last);
     const int w_lo = p.window > 0 ? max(0, w_first - p.window + 1) : 0;
     const bool idle = warp * 16 >= nrows || c0 > w_last || c0 + FN - 1 < w_lo;
     if (!idle) {
@@ -710,6 +726,23 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnParams p
     }
     __syncthreads();                  // this stage is free for the copies of the tile after the next
   }
+  if (S > 1) {
+    // this split's share of every (token, head): unnormalised output, running max, running sum (a split without keys
+    // leaves max -inf and sum 0)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      if (!(half ? okB : okA)) continue;
+      const int head = g * nrows + (half ? rB : rA);
+      float* pt = p.part + ((static_cast<size_t>(blockIdx.x) * p.H + head) * S + sidx) * (dv + 2);
+#pragma unroll
+      for (int n = 0; n < F_NT; ++n) {
+        const int d = n * 8 + (lane & 3) * 2;
+        if (d < dv) { pt[d] = o[n][2 * half]; pt[d + 1] = o[n][2 * half + 1]; }
+      }
+      if ((lane & 3) == 0) { pt[dv] = half ? mB : mA; pt[dv + 1] = half ? lB : lA; }
+    }
+    return;
+  }
   const float iA = okA ? 1.f / lA : 0.f, iB = okB ? 1.f / lB : 0.f;
   __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
 #pragma unroll
@@ -719,14 +752,15 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnParams p
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         if (!(half ? okB : okA)) continue;
-        const int t = row0 + (half ? rB : rA);
+        const int t = row0 + (half ? rB : rA);          // (row_heads: token * H + head)
         float x0 = o[n][2 * half] * (half ? iB : iA), x1 = o[n][2 * half + 1] * (half ? iB : iA);
         if (p.gate) {
-          const float* gt = p.gate + static_cast<size_t>(t) * p.ld_gate + h * dv + d;
+          const float* gt = p.row_heads ? p.gate + static_cast<size_t>(t / p.H) * p.ld_gate + (t % p.H) * dv + d
+                                        : p.gate + static_cast<size_t>(t) * p.ld_gate + h * dv + d;
           x0 *= 1.f / (1.f + expf(-gt[0]));
           x1 *= 1.f / (1.f + expf(-gt[1]));
         }
-        *reinterpret_cast<uint32_t*>(out + static_cast<size_t>(t) * p.H * dv + h * dv + d) = pack_bf16(x0, x1);
+        *reinterpret_cast<uint32_t*>(out + static_cast<size_t>(t) * HH * dv + h * dv + d) = pack_bf16(x0, x1);
       }
     }
   }
@@ -783,17 +817,34 @@ int vb_latent_norm_append(const float* d_proj, int ldp, int q_off, int c_off, in
 int vb_window_attn(void* d_out, const void* d_q, const void* d_k_cache, const void* d_v_cache, const float* d_gate,
                    int ld_gate, const int32_t* d_row_req, const int32_t* d_pos, const int32_t* d_page_indptr,
                    const int32_t* d_page_indices, int T, int H, int G, int dim, int vdim, int page_size, int window,
-                   float scale, int dtype, float* d_part, long long part_floats, const int32_t* d_row_list, void* stream) {
+                   float scale, int dtype, float* d_part, long long part_floats, const int32_t* d_row_list, int head_rows,
+                   void* stream) {
   VB_CHECK_ARG(d_out && d_q && d_k_cache && d_v_cache && d_row_req && d_pos && d_page_indptr && d_page_indices,
                "vb_window_attn: null pointer");
   VB_CHECK_ARG(H > 0 && G > 0 && H % G == 0 && dim > 0 && vdim > 0 && vdim <= 32 * WA_MAXU && page_size > 0,
                "vb_window_attn: bad sizes H=%d G=%d dim=%d vdim=%d (vdim <= %d)", H, G, dim, vdim, 32 * WA_MAXU);
   if (T <= 0) return 0;
   WindowAttnParams p{d_q, d_k_cache, d_v_cache, d_out, d_gate, ld_gate, d_row_req, d_pos, d_page_indptr, d_page_indices,
-                     nullptr, nullptr, nullptr, T, H, G, dim, vdim, page_size, window, scale, d_row_list, 1, d_part};
+                     nullptr, nullptr, nullptr, T, H, G, dim, vdim, page_size, window, scale, d_row_list, 0, 1, d_part};
+  const int R = H / G;
+  // head_rows: the query heads that share a key/value head become the rows of a tensor-core tile (bf16, head sizes the
+  // tile kernel takes, 2 .. 64 heads per group): the group's K / V tiles are staged once and multiplied on the tensor cores
+  if (head_rows && dtype == 0 && R >= 2 && R <= FM && dim % 16 == 0 && vdim % 16 == 0 && dim <= 16 * F_KB && vdim <= 8 * F_NT) {
+    int splits = 1;
+    if (d_part) {
+      splits = max(1, min(8, (2 * 148) / max(1, T * G)));
+      while (splits > 1 && static_cast<long long>(T) * H * splits * (vdim + 2) > part_floats) --splits;
+    }
+    p.row_heads = 1;
+    p.splits = splits;
+    const size_t msmem = 2 * static_cast<size_t>(FN) * (dim + 8 + vdim + 8) * sizeof(__nv_bfloat16);
+    VB_CHECK_CUDA(cudaFuncSetAttribute(window_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+    VB_LAUNCH_PDL(window_attn_mma_kernel, dim3(T, G, splits), 128, msmem, stream, p);
+    if (splits > 1) VB_LAUNCH_PDL(window_attn_merge_kernel<bf16>, dim3(T, H), 64, 0, stream, p);
+    return 0;
+  }
   // a CTA per (row, key/value head) with the K / V tiles shared by the group's query heads, when the group fits its
   // registers and the tiles fit shared memory; one warp per (row, query head) otherwise
-  const int R = H / G;
   const size_t gsmem = (static_cast<size_t>(R) * dim + static_cast<size_t>(WD_KEYS) * (dim + 1 + vdim + 1) +
                         static_cast<size_t>(R) * WD_KEYS) * sizeof(float);
   if (R <= 4 * WD_RU && vdim <= 32 * WD_VU && gsmem <= 96 * 1024) {
@@ -838,7 +889,7 @@ int vb_window_attn_tiled(void* d_out, const void* d_q, const void* d_k_cache, co
                "vb_window_attn_tiled: bad sizes H=%d G=%d dim=%d vdim=%d", H, G, dim, vdim);
   if (n_tiles <= 0) return 0;
   WindowAttnParams p{d_q, d_k_cache, d_v_cache, d_out, d_gate, ld_gate, nullptr, d_pos, d_page_indptr, d_page_indices,
-                     d_qo_indptr, d_tile_req, d_tile_row0, T, H, G, dim, vdim, page_size, window, scale, nullptr, 1, nullptr};
+                     d_qo_indptr, d_tile_req, d_tile_row0, T, H, G, dim, vdim, page_size, window, scale, nullptr, 0, 1, nullptr};
   dim3 grid(n_tiles, H);
   if (dtype == 0 && dim % 16 == 0 && vdim % 16 == 0 && dim <= 16 * F_KB && vdim <= 8 * F_NT) {
     const size_t msmem = 2 * static_cast<size_t>(FN) * (dim + 8 + vdim + 8) * sizeof(__nv_bfloat16);      // two stages

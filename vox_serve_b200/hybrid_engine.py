@@ -564,7 +564,7 @@ class HybridEngine:
 
     # ---- mixers ----------------------------------------------------------------------------------------------
     def _run_attention(self, s: StepInputs, q, kc, vc, out, gate, H: int, G: int, dim: int, vdim: int, window: int,
-                       scale: float) -> None:
+                       scale: float, head_rows: bool = False) -> None:
         """Prompt portions on the tiled kernel and single-token rows on the per-row kernel (split over keys with few rows)."""
         tiles = None
         if s.tiles is not None and self.use_tiled_attention and vdim <= 256:
@@ -573,9 +573,9 @@ class HybridEngine:
         if tiles is not None and (not s.single or s.single_rows is not None):
             ops.window_attn(*args, tiles=tiles)
             if s.single:
-                ops.window_attn(*args, scratch=self.attn_part, rows=s.single_rows)
+                ops.window_attn(*args, scratch=self.attn_part, rows=s.single_rows, head_rows=head_rows)
         else:
-            ops.window_attn(*args, scratch=self.attn_part)
+            ops.window_attn(*args, scratch=self.attn_part, head_rows=head_rows)
 
     def _latent(self, i: int, m: LatentAttentionConfig, w: Dict[str, Any], s: StepInputs) -> torch.Tensor:
         """Latent attention in its absorbed form: a head's score q . (U_k c) equals (U_k^T q) . c and its output
@@ -592,7 +592,7 @@ class HybridEngine:
         q = self._proj_ct(cq, w["uq"], self.q[:T * H * m.dim].view(T, H * m.dim))
         q_lat = ops.linear_batched(q.view(T, H, m.dim), w["uk_t"], self.q_lat[:T * H * R].view(T, H, R))
         o_lat = self.o_lat[:T * H * R].view(T, H * R)
-        self._run_attention(s, q_lat.view(T, H * R), cache, cache, o_lat, None, H, 1, R, R, 0, m.scale)
+        self._run_attention(s, q_lat.view(T, H * R), cache, cache, o_lat, None, H, 1, R, R, 0, m.scale, head_rows=True)
         out = self.mix_out[:T * H * m.vdim].view(T, H, m.vdim)
         ops.linear_batched(o_lat.view(T, H, R), w["uv"], out, gate=proj[:, P - H:])
         return self._proj(out.view(T, H * m.vdim), w["o"], self.y[:T])

@@ -1100,11 +1100,13 @@ def window_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, o
                 gate: Optional[torch.Tensor], row_req: torch.Tensor, pos: torch.Tensor, page_indptr: torch.Tensor,
                 page_indices: torch.Tensor, T: int, H: int, G: int, dim: int, vdim: int, window: int, scale: float,
                 tiles: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor, int]] = None,
-                scratch: Optional[torch.Tensor] = None, rows: Optional[Tuple[torch.Tensor, int]] = None) -> torch.Tensor:
+                scratch: Optional[torch.Tensor] = None, rows: Optional[Tuple[torch.Tensor, int]] = None,
+                head_rows: bool = False) -> torch.Tensor:
     """gate: an fp32 view [T, H * vdim] (any row stride) or None.  tiles = (qo_indptr, tile_req, tile_row0, n_tiles):
     run the tiled prompt kernel over those row tiles instead of the per-row kernel.  scratch (fp32): lets the per-row kernel
     split a row's keys over several CTAs when the step has few rows.  rows = (int32 row indices, count): serve only those
-    rows (per-row kernel)."""
+    rows (per-row kernel).  head_rows: where sizes allow, single-token rows run as tensor-core tiles whose rows are the query
+    heads that share a key/value head (many heads on few key/value heads: latent attention)."""
     _need_cuda(q, k_cache, v_cache, out)
     ld_gate = gate.stride(0) if gate is not None else 0
     if tiles is None:
@@ -1112,7 +1114,7 @@ def window_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, o
         call("vb_window_attn", out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _p(gate), ld_gate,
              row_req.data_ptr(), pos.data_ptr(), page_indptr.data_ptr(), page_indices.data_ptr(), n, H, G, dim, vdim,
              k_cache.shape[1], int(window), float(scale), _dt(q), _p(scratch), scratch.numel() if scratch is not None else 0,
-             _p(rows[0]) if rows is not None else None, _stream())
+             _p(rows[0]) if rows is not None else None, int(head_rows), _stream())
     else:
         qo, tile_req, tile_row0, n_tiles = tiles
         call("vb_window_attn_tiled", out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _p(gate),
