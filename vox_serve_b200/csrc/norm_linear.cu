@@ -147,59 +147,88 @@ __global__ void __launch_bounds__(256) residual_side_kernel(ResidualSideParams p
     const WT* Wg = static_cast<const WT*>(p.side_gate);
     const WT* Wp = static_cast<const WT*>(p.side_proj);
     const bool vec = (W & 7) == 0 && (SD & 7) == 0;
-    for (int d = warp; d < SD; d += nw) {
-      const WT* wr = Wg + static_cast<size_t>(d) * W;
-      float s[ROWS];
+    // gate: a warp forms DU dot products at once (DU independent weight streams in flight per lane); every dot product is
+    // summed in the same order whatever DU and ROWS are
+    constexpr int DU = 4;
+    for (int d0 = warp * DU; d0 < SD; d0 += nw * DU) {
+      float s[DU][ROWS];
 #pragma unroll
-      for (int r = 0; r < ROWS; ++r) s[r] = 0.f;
+      for (int u = 0; u < DU; ++u)
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) s[u][r] = 0.f;
       if (vec) {
+#pragma unroll 2
         for (int i = lane * 8; i < W; i += 256) {
-          float wv[8];
-          load8<WT>(wr + i, wv);
+          float wv[DU][8];
+#pragma unroll
+          for (int u = 0; u < DU; ++u) {
+            if (d0 + u < SD) load8<WT>(Wg + static_cast<size_t>(d0 + u) * W + i, wv[u]);
+            else
+#pragma unroll
+              for (int e = 0; e < 8; ++e) wv[u][e] = 0.f;
+          }
 #pragma unroll
           for (int r = 0; r < ROWS; ++r) {
             const float4 a = *reinterpret_cast<const float4*>(row + r * W + i), b = *reinterpret_cast<const float4*>(row + r * W + i + 4);
-            float acc = s[r];
-            acc = fmaf(wv[0], a.x, acc); acc = fmaf(wv[1], a.y, acc); acc = fmaf(wv[2], a.z, acc); acc = fmaf(wv[3], a.w, acc);
-            acc = fmaf(wv[4], b.x, acc); acc = fmaf(wv[5], b.y, acc); acc = fmaf(wv[6], b.z, acc); acc = fmaf(wv[7], b.w, acc);
-            s[r] = acc;
+#pragma unroll
+            for (int u = 0; u < DU; ++u) {
+              float acc = s[u][r];
+              acc = fmaf(wv[u][0], a.x, acc); acc = fmaf(wv[u][1], a.y, acc); acc = fmaf(wv[u][2], a.z, acc); acc = fmaf(wv[u][3], a.w, acc);
+              acc = fmaf(wv[u][4], b.x, acc); acc = fmaf(wv[u][5], b.y, acc); acc = fmaf(wv[u][6], b.z, acc); acc = fmaf(wv[u][7], b.w, acc);
+              s[u][r] = acc;
+            }
           }
         }
       } else {
-        for (int i = lane; i < W; i += 32) {
-          const float wv = to_f(wr[i]);
+        for (int i = lane; i < W; i += 32)
 #pragma unroll
-          for (int r = 0; r < ROWS; ++r) s[r] = fmaf(wv, row[r * W + i], s[r]);
-        }
+          for (int u = 0; u < DU; ++u) {
+            const float wv = d0 + u < SD ? to_f(Wg[static_cast<size_t>(d0 + u) * W + i]) : 0.f;
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) s[u][r] = fmaf(wv, row[r * W + i], s[u][r]);
+          }
       }
 #pragma unroll
-      for (int r = 0; r < ROWS; ++r) {
-        const float tot = warp_sum(s[r]);
-        if (lane == 0 && r < nr) {
-          const int id = min(max(p.ids[t0 + r], 0), p.vocab - 1);
-          const WT* e = static_cast<const WT*>(p.side_embed) + static_cast<size_t>(id) * p.ld_e + p.e_off;
-          g[r * SD + d] = act_apply(tot, 4) * to_f(e[d]);
+      for (int u = 0; u < DU; ++u)
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+          const float tot = warp_sum(s[u][r]);
+          if (lane == 0 && r < nr && d0 + u < SD) {
+            const int id = min(max(p.ids[t0 + r], 0), p.vocab - 1);
+            const WT* e = static_cast<const WT*>(p.side_embed) + static_cast<size_t>(id) * p.ld_e + p.e_off;
+            g[r * SD + d0 + u] = act_apply(tot, 4) * to_f(e[d0 + u]);
+          }
         }
-      }
     }
     for (int i = threadIdx.x; i < (ROWS - nr) * SD; i += blockDim.x) g[nr * SD + i] = 0.f;
     __syncthreads();
     float q[ROWS];
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) q[r] = 0.f;
+#pragma unroll 2
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
       const WT* wr = Wp + static_cast<size_t>(i) * SD;
       float s[ROWS];
 #pragma unroll
       for (int r = 0; r < ROWS; ++r) s[r] = 0.f;
       if (vec) {
-        for (int d = 0; d < SD; d += 8) {
-          float wv[8];
-          load8<WT>(wr + d, wv);
+        // 32 weights (four 16-byte loads in flight) at a time
+        for (int d = 0; d < SD; d += 32) {
+          float wv[4][8];
 #pragma unroll
-          for (int r = 0; r < ROWS; ++r)
+          for (int c = 0; c < 4; ++c) {
+            if (d + 8 * c < SD) load8<WT>(wr + d + 8 * c, wv[c]);
+            else
 #pragma unroll
-            for (int e = 0; e < 8; ++e) s[r] = fmaf(wv[e], g[r * SD + d + e], s[r]);
+              for (int e = 0; e < 8; ++e) wv[c][e] = 0.f;
+          }
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            if (d + 8 * c < SD)
+#pragma unroll
+              for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) s[r] = fmaf(wv[c][e], g[r * SD + d + 8 * c + e], s[r]);
         }
       } else {
         for (int d = 0; d < SD; ++d) {
