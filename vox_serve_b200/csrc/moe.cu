@@ -257,7 +257,19 @@ __global__ void moe_scale_dense_kernel(__nv_bfloat16* __restrict__ act, const in
   if (shared_gate) {                // the shared expert's columns (after the experts') times the token's gate
     const float gsh = shared_gate[t];
     __nv_bfloat16* sh = act + t * ld + static_cast<size_t>(E) * ff;
-    for (int c = threadIdx.x; c < shared_ff; c += blockDim.x) sh[c] = __float2bfloat16_rn(gsh * __bfloat162float(sh[c]));
+    if ((shared_ff & 7) == 0 && (ld & 7) == 0 && ((E * ff) & 7) == 0) {
+      uint4* sh4 = reinterpret_cast<uint4*>(sh);
+      for (int v = threadIdx.x; v < shared_ff / 8; v += blockDim.x) {
+        uint4 x = sh4[v];
+        x.x = pack_bf16(gsh * bf16_lo(x.x), gsh * bf16_hi(x.x));
+        x.y = pack_bf16(gsh * bf16_lo(x.y), gsh * bf16_hi(x.y));
+        x.z = pack_bf16(gsh * bf16_lo(x.z), gsh * bf16_hi(x.z));
+        x.w = pack_bf16(gsh * bf16_lo(x.w), gsh * bf16_hi(x.w));
+        sh4[v] = x;
+      }
+    } else {
+      for (int c = threadIdx.x; c < shared_ff; c += blockDim.x) sh[c] = __float2bfloat16_rn(gsh * __bfloat162float(sh[c]));
+    }
   }
   for (int e = threadIdx.x; e < E; e += blockDim.x) we[e] = 0.f;
   __syncthreads();
