@@ -377,7 +377,7 @@ struct LinearParams {
   float alpha;
   long long x_group_stride, o_group_stride;     // batched form (both 0 otherwise)
   const float* gate;
-  int ld_gate, batched;
+  int ld_gate;
 };
 
 template <typename XT, typename WT, typename OT, int EPI>
@@ -644,7 +644,7 @@ int vb_linear_batched(void* d_out, const void* d_x, const void* d_w, int T, int 
   VB_CHECK_ARG(!d_gate || ld_gate >= groups, "vb_linear_batched: gate rows hold one value per group");
   if (T <= 0) return 0;
   LinearParams p{d_out, d_x, d_w, nullptr, nullptr, T, N, K, ldx, ldo, epilogue, w_group_stride, alpha, x_group_stride,
-                 o_group_stride, d_gate, ld_gate, 1};
+                 o_group_stride, d_gate, ld_gate};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool aligned = ldx % 8 == 0 && x_group_stride % 8 == 0 && w_group_stride % 8 == 0 && ldo % 2 == 0 && o_group_stride % 2 == 0 &&
                        reinterpret_cast<uintptr_t>(d_x) % 16 == 0 && reinterpret_cast<uintptr_t>(d_w) % 16 == 0 &&
@@ -701,7 +701,7 @@ int vb_linear(void* d_out, const void* d_x, const void* d_w, int T, int N, int K
   VB_CHECK_ARG(epilogue >= 0 && epilogue <= 4, "vb_linear: epilogue %d", epilogue);
   VB_CHECK_ARG(groups >= 1 && (groups == 1 || d_row_off), "vb_linear: grouped launches need row offsets");
   if (T <= 0) return 0;
-  LinearParams p{d_out, d_x, d_w, d_row_off, d_gather, T, N, K, ldx, ldo, epilogue, w_group_stride, alpha, 0, 0, nullptr, 0, 0};
+  LinearParams p{d_out, d_x, d_w, d_row_off, d_gather, T, N, K, ldx, ldo, epilogue, w_group_stride, alpha, 0, 0, nullptr, 0};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // in_dtype: 0 = bf16 activations and weights, 1 = fp32 both; out_dtype likewise
   if (in_dtype == 1) return out_dtype == 1 ? launch_linear<float, float, float>(p, groups, T, s) : launch_linear<float, float, bf16>(p, groups, T, s);
