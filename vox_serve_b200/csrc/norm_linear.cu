@@ -119,10 +119,11 @@ template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bflo
   v[4] = bf16_lo(a.z); v[5] = bf16_hi(a.z); v[6] = bf16_lo(a.w); v[7] = bf16_hi(a.w);
 }
 
-// ROWS rows per CTA: the side matrices are read once per CTA and serve all of its rows (long steps), every row's sums
-// are formed in the same order whatever ROWS is, so a row's result does not depend on the step it is part of.
+// ROWS rows per CTA: the side matrices are read once per CTA and serve all of its rows (long steps).  A row's result
+// depends on nothing but the row; between the one-row form (16 warps) and the four-row form (8 warps) only the order in
+// which the norms' sums of squares are added differs.
 template <typename WT, typename OT, int ROWS>
-__global__ void __launch_bounds__(256) residual_side_kernel(ResidualSideParams p) {
+__global__ void __launch_bounds__(ROWS == 1 ? 512 : 256) residual_side_kernel(ResidualSideParams p) {
   extern __shared__ float sm[];
   const int W = p.W, SD = p.side_dim;
   float* row = sm;                      // [ROWS][W]
@@ -604,7 +605,8 @@ static int launch_residual_side(const ResidualSideParams& p, int T, cudaStream_t
     VB_LAUNCH_PDL((residual_side_kernel<WT, OT, 4>), (T + 3) / 4, 256, smem, stream, p);
   } else {
     if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(residual_side_kernel<WT, OT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
-    VB_LAUNCH_PDL((residual_side_kernel<WT, OT, 1>), T, 256, smem, stream, p);
+    // (one row per CTA: 16 warps, so that more of the row's weight streams are in flight)
+    VB_LAUNCH_PDL((residual_side_kernel<WT, OT, 1>), T, 512, smem, stream, p);
   }
   return 0;
 }
