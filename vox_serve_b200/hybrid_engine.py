@@ -191,7 +191,10 @@ class HybridWeights:
     ``l<i>.norm1b[.b]``, ``l<i>.norm2[.b]``, ``l<i>.norm2b[.b]``, ``l<i>.mix.{q,k,v,g,o,vmix,norm}``,
     ``l<i>.mlp.{router,router.b,e<j>.{gate,up,down},shared.{gate,up,down}}``, ``final.norm[.b]``, ``head``.
     q | k | v | g are concatenated into one projection, gate | up of every expert into one matrix, the experts into
-    [E, ...] stacks.  Matrices take the compute dtype; norm weights, router, decays and mixing coefficients stay fp32."""
+    [E, ...] stacks.  Matrices take the compute dtype; norm weights, router, decays and mixing coefficients stay fp32.
+    Parallel blocks with RMS norms have ``l<i>.norm1``, ``l<i>.norm2`` (weights only), optionally ``pos`` (learned
+    positions), ``side.embed`` + ``l<i>.side.{gate,proj,norm}`` (per-token side input); latent-attention mixers and
+    experts without a gate matrix are described at ``_load_latent`` / ``_load_plain_moe``."""
 
     def __init__(self, sd: Dict[str, torch.Tensor], cfg: HybridConfig, dtype: torch.dtype, device,
                  tensor_core: bool = True):

@@ -1,4 +1,4 @@
-"""Worker for text-only LMs on the hybrid engine (model/bobavik.py): the same five scheduler-facing methods, page pool,
+"""Worker for text-only LMs on the hybrid engine (model/bobavik.py, model/razevik.py): the same five scheduler-facing methods, page pool,
 batch slots, packed staging buffer, sampled-id ring and decode CUDA graphs as ``ModelWorker``, with three differences.
 
   * Prompts are fed in portions.  A request carries ``pending_tokens`` (the rest of its prompt, or continuation tokens a
