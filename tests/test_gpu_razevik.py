@@ -53,6 +53,18 @@ def test_registry_picks_the_design_by_architecture():
     assert get_model_class("razevik-synthetic:3") is RazevikModel
 
 
+def test_cache_holds_one_latent_per_token_and_shares_it_between_layers():
+    from vox_serve_b200.hybrid_engine import HybridCache
+    from vox_serve_b200.model.razevik import razevik_config
+
+    c = razevik_config(O.make_config(layers=("own", "shared", "dense", "bare", "shared"), kv_rank=16))
+    cache = HybridCache(c, 5, 8, 3, torch.float32, "cpu")
+    assert tuple(cache.k[0].shape) == (5, 8, 1, 16) and cache.k[0].data_ptr() == cache.v[0].data_ptr()
+    assert cache.k[1].data_ptr() == cache.k[0].data_ptr() and cache.k[4].data_ptr() == cache.k[3].data_ptr()
+    assert len({cache.k[i].data_ptr() for i in range(5)}) == 3 and not cache.state
+    assert cache.nbytes() == 3 * 5 * 8 * 16 * 4
+
+
 def test_oracle_router_by_hand():
     """six experts in three pairs, keep two groups, top two.  Scores are set through the router rows (h = e_0)."""
     W = 4
