@@ -352,14 +352,16 @@ def test_latent_attention_far_keys_and_page_borders(tiled, dtype):
 
 # ---- the other mechanisms alone ----------------------------------------------------------------------------------------
 @pytest.mark.gpu
-def test_norms_side_input_and_batched_projection():
+@pytest.mark.parametrize("W,d,T", [(44, 5, 19), (42, 3, 7), (64, 8, 300)])
+def test_norms_side_input_and_batched_projection(W, d, T):
+    """widths and side sizes that move in 16-byte pieces and ones that cannot; 300 rows: four rows per CTA in the block tail."""
     from vox_serve_b200 import ops
 
     g = torch.Generator().manual_seed(2)
-    T, W, d, vocab, n_layers = 19, 44, 5, 23, 3
+    vocab, n_layers = 23, 3
     x = torch.randn(T, W, generator=g) * 3
     w1, w2 = torch.randn(W, generator=g), torch.randn(W, generator=g)
-    rows = torch.tensor([4, 0, 18], dtype=I32)
+    rows = torch.tensor([4, 0, T - 1], dtype=I32)
     for dt, tol in ((F32, 1e-5), (BF16, 2e-2)):
         o1, o2 = torch.zeros(T, W, dtype=dt, device=DEV), torch.zeros(T, W, dtype=dt, device=DEV)
         ops.rmsnorm2_f32(x.to(DEV), w1.to(DEV), 1e-3, o1, w2.to(DEV), o2)

@@ -523,21 +523,25 @@ __global__ void __launch_bounds__(128) window_attn_group_kernel(WindowAttnParams
 // merges the splits of a (row, head): out = sum_s acc_s e^(m_s - M) / sum_s l_s e^(m_s - M), then the gate
 template <typename CT>
 __global__ void __launch_bounds__(64) window_attn_merge_kernel(WindowAttnParams p) {
+  __shared__ float wgt[32];       // e^(m_s - M) / L of every split (at most 32 splits)
   pdl_sync();
   const int ti = blockIdx.x, h = blockIdx.y, S = p.splits, dv = p.vdim;
   const int t = p.row_list ? p.row_list[ti] : ti;
   const float* pt = p.part + (static_cast<size_t>(ti) * p.H + h) * S * (dv + 2);
-  float M = -INFINITY;
-  for (int s = 0; s < S; ++s) M = fmaxf(M, pt[s * (dv + 2) + dv]);
-  float L = 0.f;
-  for (int s = 0; s < S; ++s) L += pt[s * (dv + 2) + dv + 1] * expf(pt[s * (dv + 2) + dv] - M);
-  const float inv = 1.f / L;
+  if (threadIdx.x < 32) {
+    const int s = threadIdx.x;
+    const float m = s < S ? pt[s * (dv + 2) + dv] : -INFINITY, l = s < S ? pt[s * (dv + 2) + dv + 1] : 0.f;
+    const float M = warp_max(m);
+    const float w = m == -INFINITY ? 0.f : expf(m - M);
+    const float L = warp_sum(l * w);
+    wgt[s] = w / L;
+  }
+  __syncthreads();
   CT* out = static_cast<CT*>(p.out) + static_cast<size_t>(t) * p.H * dv + h * dv;
   const float* gate = p.gate ? p.gate + static_cast<size_t>(t) * p.ld_gate + h * dv : nullptr;
   for (int d = threadIdx.x; d < dv; d += blockDim.x) {
-    float a = 0.f;
-    for (int s = 0; s < S; ++s) a += pt[s * (dv + 2) + d] * expf(pt[s * (dv + 2) + dv] - M);
-    float o = a * inv;
+    float o = 0.f;
+    for (int s = 0; s < S; ++s) o = fmaf(pt[s * (dv + 2) + d], wgt[s], o);
     if (gate) o *= 1.f / (1.f + expf(-gate[d]));
     out[d] = wa_from_f<CT>(o);
   }
