@@ -228,10 +228,10 @@ class HybridWeights:
                 return ops.pack_weight(ops.interleave_gate_up(mat(gate_name), mat(up_name), half), 2 * half)
             return mat(gate_name, up_name)
 
-        self._mat, self._vec, self._dense = mat, vec, dense
-        rms = cfg.norm == "rmsnorm"
-        if rms:
-            norm = lambda name: (vec(name), None)                      # noqa: E731
+        self._mat, self._vec, self._dense = mat, vec, dense      # (for the per-mechanism loaders below; dropped at the end)
+        if cfg.norm == "rmsnorm":
+            def norm(name):                                        # noqa: F811  (weight only)
+                return vec(name), None
         self.embed = mat("embed")
         self.head = dense(mat("head"))
         self.final_norm = norm("final.norm")
